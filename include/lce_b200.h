@@ -1,0 +1,139 @@
+/*
+ * lce_b200 -- C ABI of the B200 (sm_100a) fused linear + cross-entropy library.
+ *
+ * This is the operator boundary of the hot path
+ *     loss = cross_entropy(logit_scale * (x @ W), y) + z_regularization * mean(logsumexp^2)
+ * computed N_chunk rows at a time, with both gradients produced during the forward pass.
+ * It replaces the two Triton launches and the host-side torch reductions that the reference
+ * performs once per row chunk (linear_cross_entropy/ops.py:721-791 in the reference project).
+ *
+ * Conventions
+ *   - Plain C: pointers, sizes, PODs. No C++/torch types cross this boundary.
+ *   - Every pointer named dev_* / x / weight / labels / workspace ... is a DEVICE pointer.
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, nothing synchronises
+ *     (except lce_read_status, which is a debugging call).
+ *   - The library never allocates device memory: the caller passes one workspace blob sized by
+ *     lce_workspace_bytes().
+ *   - Every entry point returns an int status: LCE_OK or a negative LCE_ERR_* code;
+ *     lce_status_string() maps it to text.  No exception crosses the ABI.
+ *   - W is stored (hidden, vocab) with the vocab index contiguous, like the reference's
+ *     transposed nn.Linear weight (ops.py:913).
+ *
+ * Shapes: rows per chunk % 128 == 0, hidden % 256 == 0, vocab_local % 256 == 0
+ * (the reference asserts N % 512, V % 4096, H % 256: ops.py:689-691).
+ */
+#ifndef LCE_B200_H
+#define LCE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LCE_OK 0
+#define LCE_ERR_INVALID_ARGUMENT (-1)
+#define LCE_ERR_UNSUPPORTED_SHAPE (-2)
+#define LCE_ERR_MISALIGNED (-3)
+#define LCE_ERR_UNSUPPORTED_DEVICE (-4)
+#define LCE_ERR_CUDA (-5)
+#define LCE_ERR_DEVICE_TIMEOUT (-6)
+#define LCE_ERR_DRIVER (-7)
+#define LCE_ERR_TOO_LARGE (-8)
+
+/* element types of x / W (and of the exp slab the forward writes) */
+#define LCE_DTYPE_F16 0
+#define LCE_DTYPE_BF16 1
+#define LCE_DTYPE_F32 2 /* multiplied as TF32, like tl.dot on fp32 inputs in the reference */
+
+/* One problem description shared by all calls of one forward+backward pass. */
+typedef struct lce_problem {
+  int64_t n_rows_total;   /* N = B*S, all chunks                                  */
+  int64_t chunk_rows;     /* rows per chunk, min(N, N_chunk_size) (ops.py:687)    */
+  int64_t hidden;         /* H = in_features                                       */
+  int64_t vocab_local;    /* columns of W held by this rank (V when not sharded)  */
+  int64_t vocab_offset;   /* class id of local column 0 (0 when not sharded)      */
+  int64_t ignore_index;   /* rows with this label do not count (ops.py:705)       */
+  int32_t world;          /* number of vocab shards whose row statistics are combined */
+  int32_t dtype;          /* LCE_DTYPE_* of x and W                                */
+  int32_t monitoring;     /* 1: also produce logit max / entropy / norm            */
+  int32_t want_grad;      /* 0: forward only (no slab is written)                  */
+  float logit_scale;      /* z = logit_scale * (x @ W)  (ops.py:200)               */
+  float z_regularization; /* weight of mean(lse^2)       (ops.py:756-761)          */
+} lce_problem;
+
+/* Number of per-row partial statistics a rank exports per chunk (max, sumexp, target logit,
+ * sum exp*z, sum z^2); lce_forward_chunk writes LCE_ROW_PARTS * chunk_rows floats. */
+#define LCE_ROW_PARTS 5
+
+/* ---- housekeeping ------------------------------------------------------------------------- */
+int lce_version(void);
+const char* lce_status_string(int status);
+/* Kernels launched by this library in this process so far (all threads). */
+long long lce_launch_count(void);
+
+/* Bytes of workspace one pass needs for `p` (slab + statistics + split-K partials + scalars).
+ * Replaces the per-call torch allocations of ops.py:697-703. */
+int lce_workspace_bytes(const lce_problem* p, size_t* bytes);
+
+/* ---- the pass, in call order ------------------------------------------------------------------
+ * lce_begin            once:      counts valid labels (ops.py:705), clears the loss accumulators
+ * per chunk:
+ *   lce_forward_chunk             logit GEMM + softmax statistics + exp slab (ops.py:722-752)
+ *   [sharded: all-gather the row partials of all ranks]
+ *   lce_combine_chunk             log-sum-exp per row, loss / metric sums (ops.py:753-761)
+ *   lce_backward_chunk            dZ, dx rows of the chunk, dW accumulation (ops.py:763-791)
+ *   [sharded: all-reduce the chunk's dx rows]
+ * lce_finalize         once:      5 scalars (ops.py:793-802)
+ */
+int lce_begin(const lce_problem* p, const int64_t* labels, void* workspace, void* stream);
+
+/* x: [n_rows_total, hidden] with row stride x_ld elements; weight: [hidden, vocab_local] with row
+ * stride w_ld elements; labels: [n_rows_total]. Processes rows [row0, row0 + rows).
+ * row_parts_local: float[LCE_ROW_PARTS * chunk_rows] output (this rank's per-row partials). */
+int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
+                      const int64_t* labels, int64_t row0, int64_t rows, void* workspace,
+                      float* row_parts_local, void* stream);
+
+/* row_parts_all: float[world * LCE_ROW_PARTS * chunk_rows], rank-major (for world == 1 this is
+ * row_parts_local). */
+int lce_combine_chunk(const lce_problem* p, const float* row_parts_all, const int64_t* labels, int64_t row0,
+                      int64_t rows, void* workspace, void* stream);
+
+/* dx: [n_rows_total, hidden] (row stride dx_ld, element type dx_dtype = LCE_DTYPE_*), rows
+ * [row0, row0+rows) are written. dweight: float[hidden, vocab_local] (row stride dw_ld), overwritten
+ * when first_chunk != 0, else accumulated into. Both gradients are those of the mean loss
+ * (already multiplied by logit_scale / n_valid, ops.py:332,443). */
+int lce_backward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
+                       const int64_t* labels, int64_t row0, int64_t rows, void* workspace, void* dx,
+                       int64_t dx_ld, int32_t dx_dtype, float* dweight, int64_t dw_ld, int32_t first_chunk,
+                       void* stream);
+
+/* out5: float[5] = loss, z_value, logit_max, logit_entropy, logit_norm (the reference's return
+ * tuple, ops.py:802). The last three are only meaningful with monitoring. If any kernel of the pass
+ * reported a device-side error the loss is NaN. */
+int lce_finalize(const lce_problem* p, void* workspace, float* out5, void* stream);
+
+/* dst[r, c] = src[r, c] * (*dev_factor), converting element type (the reference's
+ * x_grad.mul_(grad_output), ops.py:810). src == dst is allowed when the types match. */
+int lce_grad_scale_cast(const void* src, int32_t src_dtype, int64_t src_ld, void* dst, int32_t dst_dtype,
+                        int64_t dst_ld, int64_t rows, int64_t cols, const float* dev_factor, void* stream);
+
+/* Synchronises `stream` and returns the pass's device status word translated to an LCE_* code
+ * (LCE_ERR_DEVICE_TIMEOUT if a bounded in-kernel wait ran out). Debugging / tests. */
+int lce_read_status(void* workspace, void* stream);
+
+/* ---- diagnostics ------------------------------------------------------------------------------
+ * Runs the GEMM engine alone: out[s][M, N] = A * B^T over K-split s (fp32, row stride N).
+ * a_mn_major == 0: a is [M, K] (K contiguous, row stride a_ld); != 0: a is [K, M] (row stride a_ld).
+ * Same for b with N. M % 128 == 0, N % 256 == 0, K % (splits * 128 bytes) == 0.
+ * dev_status: int[1] device word. No counterpart in the reference. */
+int lce_debug_gemm(int32_t dtype, int32_t a_mn_major, int32_t b_mn_major, const void* a, int64_t a_ld,
+                   const void* b, int64_t b_ld, float* out, int64_t m, int64_t n, int64_t k, int32_t splits,
+                   int* dev_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LCE_B200_H */

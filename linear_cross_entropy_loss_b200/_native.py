@@ -1,0 +1,147 @@
+"""ctypes binding of ``liblce_b200.so`` (the C ABI declared in ``include/lce_b200.h``).
+
+The shared library is built in-tree by :func:`build` (``nvcc`` for sm_100a) and loaded with
+``ctypes``; there is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import shutil
+import subprocess
+import threading
+from pathlib import Path
+
+_PKG_DIR = Path(__file__).resolve().parent
+_CSRC = _PKG_DIR / "csrc"
+_INCLUDE = _PKG_DIR.parent / "include"
+LIB_PATH = _PKG_DIR / "liblce_b200.so"
+
+LCE_OK = 0
+DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
+ROW_PARTS = 5
+
+_lock = threading.Lock()
+_lib = None
+
+
+class LceError(RuntimeError):
+    """A call into liblce_b200 returned a non-zero status."""
+
+    def __init__(self, status: int, message: str, where: str):
+        super().__init__(f"{where}: {message} (status {status})")
+        self.status = status
+
+
+class Problem(ctypes.Structure):
+    """Mirror of ``lce_problem`` (include/lce_b200.h)."""
+
+    _fields_ = [
+        ("n_rows_total", ctypes.c_int64),
+        ("chunk_rows", ctypes.c_int64),
+        ("hidden", ctypes.c_int64),
+        ("vocab_local", ctypes.c_int64),
+        ("vocab_offset", ctypes.c_int64),
+        ("ignore_index", ctypes.c_int64),
+        ("world", ctypes.c_int32),
+        ("dtype", ctypes.c_int32),
+        ("monitoring", ctypes.c_int32),
+        ("want_grad", ctypes.c_int32),
+        ("logit_scale", ctypes.c_float),
+        ("z_regularization", ctypes.c_float),
+    ]
+
+
+def _sources():
+    return sorted(list(_CSRC.glob("*.cu")) + list(_CSRC.glob("*.cuh")) + list(_INCLUDE.glob("*.h")))
+
+
+def needs_build() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    built = LIB_PATH.stat().st_mtime
+    return any(src.stat().st_mtime > built for src in _sources())
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile the CUDA sources for sm_100a into ``liblce_b200.so`` next to this file."""
+    if not force and not needs_build():
+        return LIB_PATH
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise RuntimeError("nvcc not found: liblce_b200.so cannot be built")
+    tmp = LIB_PATH.with_suffix(".so.tmp")
+    cmd = [
+        nvcc,
+        "-gencode", "arch=compute_100a,code=sm_100a",
+        "-O3", "-lineinfo", "-std=c++17",
+        "-shared", "-Xcompiler", "-fPIC",
+        "-I", str(_INCLUDE),
+        "-o", str(tmp),
+        str(_CSRC / "lce_api.cu"),
+    ]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+    os.replace(tmp, LIB_PATH)
+    if verbose:
+        print(proc.stderr)
+    return LIB_PATH
+
+
+_vp = ctypes.c_void_p
+_i64 = ctypes.c_int64
+_i32 = ctypes.c_int32
+
+# name -> (restype, argtypes); kept in one table so that a test can check it against the header.
+SIGNATURES = {
+    "lce_version": (ctypes.c_int, []),
+    "lce_status_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "lce_launch_count": (ctypes.c_longlong, []),
+    "lce_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(Problem), ctypes.POINTER(ctypes.c_size_t)]),
+    "lce_begin": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _vp, _vp]),
+    "lce_forward_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _vp, _vp]),
+    "lce_combine_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _vp, _i64, _i64, _vp, _vp]),
+    "lce_backward_chunk": (
+        ctypes.c_int,
+        [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _vp, _i64, _i32, _vp, _i64, _i32, _vp],
+    ),
+    "lce_finalize": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _vp, _vp]),
+    "lce_grad_scale_cast": (ctypes.c_int, [_vp, _i32, _i64, _vp, _i32, _i64, _i64, _i64, _vp, _vp]),
+    "lce_read_status": (ctypes.c_int, [_vp, _vp]),
+    "lce_debug_gemm": (
+        ctypes.c_int,
+        [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _vp, _vp],
+    ),
+}
+
+
+def load():
+    """Load (building first if the sources are newer) and return the ctypes library handle."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            if needs_build():
+                build()
+            lib = ctypes.CDLL(str(LIB_PATH))
+            for name, (restype, argtypes) in SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.restype = restype
+                fn.argtypes = argtypes
+            _lib = lib
+    return _lib
+
+
+def status_string(status: int) -> str:
+    return load().lce_status_string(status).decode()
+
+
+def check(status: int, where: str) -> None:
+    if status != LCE_OK:
+        raise LceError(status, status_string(status), where)
+
+
+def launch_count() -> int:
+    return int(load().lce_launch_count())

@@ -1,0 +1,357 @@
+// Memory-bound helper kernels around the three tensor-core contractions:
+//   begin_kernel        count valid labels, clear the pass accumulators
+//   row_stats_kernel    per row: merge the per-V-tile (max, sumexp, ...) into one partial per rank
+//   combine_kernel      per row: merge the ranks' partials -> log-sum-exp; accumulate loss/metric sums
+//   dz_transform_kernel slab: exp(z - tile max) -> dZ = softmax * (1 + 2 z_reg lse) - onehot, in place
+//   dx_reduce_kernel    sum the K-split partials of dx in a fixed order, cast
+//   finalize_kernel     the five output scalars
+//   scale_cast_kernel   grad * factor with a type conversion
+// All reductions run in a fixed order (no atomics), so results are bitwise reproducible.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace lce {
+
+struct PassScalars {
+  double sum_nll;    // sum over valid rows of (lse - target logit)
+  double sum_lse2;   // sum over valid rows of lse^2
+  double sum_ent;    // sum over valid rows of softmax entropy
+  double sum_norm;   // sum over ALL rows of ||z_i||_2
+  float max_logit;   // max over ALL rows and columns of z
+  float n_valid;     // number of rows whose label is not ignore_index
+  int status;        // device status word, 0 = ok
+  int pad;
+};
+
+constexpr int ROW_PARTS = 5;  // max, sumexp, target logit, sum exp*z, sum z^2
+
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ double block_sum_double(double v, double* scratch /*[32]*/) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  double t = 0.0;
+  if (warp == 0) {
+    t = (lane < (blockDim.x >> 5)) ? scratch[lane] : 0.0;
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_down_sync(0xffffffffu, t, o);
+  }
+  return t;  // valid in thread 0
+}
+__device__ __forceinline__ float block_max_float(float v, float* scratch /*[32]*/) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_down_sync(0xffffffffu, v, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = -INFINITY;
+  if (warp == 0) {
+    t = (lane < (blockDim.x >> 5)) ? scratch[lane] : -INFINITY;
+    for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_down_sync(0xffffffffu, t, o));
+  }
+  return t;
+}
+
+// One block. Counts labels != ignore_index and resets the accumulators of the pass.
+__global__ void begin_kernel(const long long* __restrict__ labels, long long n, long long ignore_index,
+                             PassScalars* sc) {
+  __shared__ double scratch[32];
+  double cnt = 0.0;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) cnt += (labels[i] != ignore_index) ? 1.0 : 0.0;
+  const double total = block_sum_double(cnt, scratch);
+  if (threadIdx.x == 0) {
+    sc->sum_nll = 0.0;
+    sc->sum_lse2 = 0.0;
+    sc->sum_ent = 0.0;
+    sc->sum_norm = 0.0;
+    sc->max_logit = -INFINITY;
+    sc->n_valid = (float)total;
+    sc->status = 0;
+    sc->pad = 0;
+  }
+}
+
+// Merges (m2, s2, u2) into the running (m, s, u):  s = sum exp(z - m),  u = sum exp(z - m) * z.
+__device__ __forceinline__ void lse_merge(float& m, float& s, float& u, float m2, float s2, float u2) {
+  if (m2 > m) {
+    const float f = __expf(m - m2);  // m = -inf on the first merge -> f = 0
+    s = s * f + s2;
+    u = u * f + u2;
+    m = m2;
+  } else {
+    const float f = __expf(m2 - m);
+    s += s2 * f;
+    u += u2 * f;
+  }
+}
+
+// Block = 32 rows x 8 warps; warp w walks V tiles w, w+8, ...; lane = row. Per-tile statistics are
+// stored [tile][row], so each warp load is 128 contiguous bytes.
+// parts layout: [ROW_PARTS][stat_ld].
+template <bool kMonitor>
+__global__ void __launch_bounds__(256)
+row_stats_kernel(const float* __restrict__ tile_max, const float* __restrict__ tile_sum,
+                 const float* __restrict__ tile_ez, const float* __restrict__ tile_sq,
+                 const float* __restrict__ target_logit, const long long* __restrict__ labels, int rows,
+                 int n_tiles, long long stat_ld, long long ignore_index, long long vocab_offset,
+                 long long vocab_local, float* __restrict__ parts) {
+  __shared__ float sm[8][4][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 32 + lane;
+  float m = -INFINITY, s = 0.f, u = 0.f, q = 0.f;
+  if (r < rows) {
+    for (int t = warp; t < n_tiles; t += 8) {
+      const long long i = (long long)t * stat_ld + r;
+      const float mt = tile_max[i], st = tile_sum[i];
+      const float ut = kMonitor ? tile_ez[i] : 0.f;
+      if (kMonitor) q += tile_sq[i];
+      lse_merge(m, s, u, mt, st, ut);
+    }
+  }
+  sm[warp][0][lane] = m;
+  sm[warp][1][lane] = s;
+  sm[warp][2][lane] = u;
+  sm[warp][3][lane] = q;
+  __syncthreads();
+  if (warp == 0 && r < rows) {
+    for (int w = 1; w < 8; ++w) {
+      lse_merge(m, s, u, sm[w][0][lane], sm[w][1][lane], sm[w][2][lane]);
+      q += sm[w][3][lane];
+    }
+    const long long yv = labels[r];
+    const long long yl = yv - vocab_offset;
+    const bool own = (yv != ignore_index) && yl >= 0 && yl < vocab_local;
+    parts[0 * stat_ld + r] = m;
+    parts[1 * stat_ld + r] = s;
+    parts[2 * stat_ld + r] = own ? target_logit[r] : 0.f;
+    parts[3 * stat_ld + r] = u;
+    parts[4 * stat_ld + r] = q;
+  }
+}
+
+// One block of 1024 threads per chunk. parts_all: [world][ROW_PARTS][stat_ld].
+__global__ void __launch_bounds__(1024)
+combine_kernel(const float* __restrict__ parts_all, int world, const long long* __restrict__ labels, int rows,
+               long long stat_ld, long long ignore_index, int monitoring, float* __restrict__ lse_out,
+               PassScalars* sc) {
+  __shared__ double scratch_d[32];
+  __shared__ float scratch_f[32];
+  double a_nll = 0.0, a_lse2 = 0.0, a_ent = 0.0, a_norm = 0.0;
+  float a_max = -INFINITY;
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+    float m = -INFINITY, s = 0.f, u = 0.f, t = 0.f, q = 0.f;
+    for (int g = 0; g < world; ++g) {
+      const float* pg = parts_all + (long long)g * ROW_PARTS * stat_ld;
+      lse_merge(m, s, u, pg[0 * stat_ld + r], pg[1 * stat_ld + r], pg[3 * stat_ld + r]);
+      t += pg[2 * stat_ld + r];
+      q += pg[4 * stat_ld + r];
+    }
+    const float lse = m + logf(s);
+    lse_out[r] = lse;
+    const bool valid = labels[r] != ignore_index;
+    if (valid) {
+      a_nll += (double)lse - (double)t;
+      a_lse2 += (double)lse * (double)lse;
+      if (monitoring) a_ent += (double)lse - (double)u / (double)s;
+    }
+    if (monitoring) {
+      a_norm += sqrt((double)q);
+      a_max = fmaxf(a_max, m);
+    }
+  }
+  const double t_nll = block_sum_double(a_nll, scratch_d);
+  const double t_lse2 = block_sum_double(a_lse2, scratch_d);
+  const double t_ent = block_sum_double(a_ent, scratch_d);
+  const double t_norm = block_sum_double(a_norm, scratch_d);
+  const float t_max = block_max_float(a_max, scratch_f);
+  if (threadIdx.x == 0) {
+    sc->sum_nll += t_nll;
+    sc->sum_lse2 += t_lse2;
+    sc->sum_ent += t_ent;
+    sc->sum_norm += t_norm;
+    sc->max_logit = fmaxf(sc->max_logit, t_max);
+  }
+}
+
+__global__ void finalize_kernel(const PassScalars* sc, double n_rows_total, float z_regularization,
+                                float* __restrict__ out5) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const double R = (double)sc->n_valid;
+  double loss = (sc->sum_nll + (double)z_regularization * sc->sum_lse2) / R;  // R == 0 -> NaN, as in the reference
+  if (sc->status != 0) loss = NAN;
+  out5[0] = (float)loss;
+  out5[1] = (float)(sc->sum_lse2 / R);
+  out5[2] = sc->max_logit;
+  out5[3] = (float)(sc->sum_ent / R);
+  out5[4] = (float)(sc->sum_norm / n_rows_total);
+}
+
+// ---------------------------------------------------------------------------------------------
+// slab transform: one warp per (row, V tile) segment of 256 elements, 8 elements per lane.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+struct Vec8 {};
+template <>
+struct Vec8<__half> {
+  uint4 raw;
+  __device__ void load(const __half* p) { raw = *reinterpret_cast<const uint4*>(p); }
+  __device__ void store(__half* p) const { *reinterpret_cast<uint4*>(p) = raw; }
+  __device__ void to_float(float (&f)[8]) const {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 v = __half22float2(h[i]);
+      f[2 * i] = v.x;
+      f[2 * i + 1] = v.y;
+    }
+  }
+  __device__ void from_float(const float (&f)[8]) {
+    __half2* h = reinterpret_cast<__half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+  }
+};
+template <>
+struct Vec8<__nv_bfloat16> {
+  uint4 raw;
+  __device__ void load(const __nv_bfloat16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+  __device__ void store(__nv_bfloat16* p) const { *reinterpret_cast<uint4*>(p) = raw; }
+  __device__ void to_float(float (&f)[8]) const {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 v = __bfloat1622float2(h[i]);
+      f[2 * i] = v.x;
+      f[2 * i + 1] = v.y;
+    }
+  }
+  __device__ void from_float(const float (&f)[8]) {
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  }
+};
+template <>
+struct Vec8<float> {
+  float4 a, b;
+  __device__ void load(const float* p) {
+    a = *reinterpret_cast<const float4*>(p);
+    b = *reinterpret_cast<const float4*>(p + 4);
+  }
+  __device__ void store(float* p) const {
+    *reinterpret_cast<float4*>(p) = a;
+    *reinterpret_cast<float4*>(p + 4) = b;
+  }
+  __device__ void to_float(float (&f)[8]) const {
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  __device__ void from_float(const float (&f)[8]) {
+    a = make_float4(f[0], f[1], f[2], f[3]);
+    b = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+
+// dZ[i, j] = valid_i * ( e[i, j] * exp(tile_max[i, tile(j)] - lse_i) * (1 + 2 z_reg lse_i) - [j == y_i] )
+// rounded to the input element type, unscaled (logit_scale / n_valid is applied to the fp32
+// accumulators of the two gradient GEMMs, as the reference does).
+// Work item = (group of 8 rows, V tile); the 8 warps of a block take the 8 rows of the group.
+template <typename T>
+__global__ void __launch_bounds__(256)
+dz_transform_kernel(T* __restrict__ slab, long long slab_ld, const float* __restrict__ tile_max,
+                    const float* __restrict__ lse, const long long* __restrict__ labels, int rows, int n_tiles,
+                    long long stat_ld, long long ignore_index, long long vocab_offset, float z_regularization) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long items = (long long)(rows / 8) * n_tiles;
+  for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+    const int tile = (int)(item % n_tiles);
+    const int r = (int)(item / n_tiles) * 8 + warp;
+    const long long yv = labels[r];
+    const bool valid = (yv != ignore_index);
+    const float lse_r = lse[r];
+    const float coef =
+        valid ? __expf(tile_max[(long long)tile * stat_ld + r] - lse_r) * (1.f + 2.f * z_regularization * lse_r)
+              : 0.f;
+    const long long ycol = yv - vocab_offset - (long long)tile * 256;
+    T* ptr = slab + (long long)r * slab_ld + (long long)tile * 256 + lane * 8;
+    Vec8<T> v;
+    v.load(ptr);
+    float f[8];
+    v.to_float(f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] *= coef;
+    if (valid && ycol >= 0 && ycol < 256 && (int)(ycol >> 3) == lane) {
+      const int sel = (int)(ycol & 7);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i == sel) f[i] -= 1.f;
+    }
+    v.from_float(f);
+    v.store(ptr);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ T cast_from_float(float v);
+template <>
+__device__ __forceinline__ float cast_from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half cast_from_float<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 cast_from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T>
+__device__ __forceinline__ float cast_to_float(T v);
+template <>
+__device__ __forceinline__ float cast_to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float cast_to_float<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float cast_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// dx[r, h] = sum_s part[s][r][h]  (fixed order s = 0, 1, ...), cast to T. cols % 4 == 0.
+template <typename T>
+__global__ void __launch_bounds__(256)
+dx_reduce_kernel(const float* __restrict__ part, int splits, long long split_stride, int rows, int cols,
+                 T* __restrict__ dx, long long dx_ld) {
+  const long long quads = (long long)rows * (cols / 4);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < quads;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / (cols / 4);
+    const int c = (int)(i % (cols / 4)) * 4;
+    float4 acc = *reinterpret_cast<const float4*>(part + r * cols + c);
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(part + (long long)s * split_stride + r * cols + c);
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    T* d = dx + r * dx_ld + c;
+    d[0] = cast_from_float<T>(acc.x);
+    d[1] = cast_from_float<T>(acc.y);
+    d[2] = cast_from_float<T>(acc.z);
+    d[3] = cast_from_float<T>(acc.w);
+  }
+}
+
+template <typename S, typename D>
+__global__ void __launch_bounds__(256)
+scale_cast_kernel(const S* src, long long src_ld, D* dst, long long dst_ld, long long rows,
+                  long long cols, const float* __restrict__ factor) {
+  const float f = *factor;
+  const long long n = rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols, c = i % cols;
+    dst[r * dst_ld + c] = cast_from_float<D>(cast_to_float<S>(src[r * src_ld + c]) * f);
+  }
+}
+
+}  // namespace lce

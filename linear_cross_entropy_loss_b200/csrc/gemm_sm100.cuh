@@ -1,0 +1,460 @@
+// Persistent, warp-specialised tcgen05 GEMM engine for sm_100a.
+//
+//   D[M, N] = A[M, K] * B[N, K]^T        (fp32 accumulation in tensor memory)
+//
+// One CTA per SM walks a static list of 128 x 256 output tiles. Inside a CTA:
+//   warp 0      TMA producer: fills a 4-deep ring of (A tile, B tile) K-blocks in shared memory
+//   warp 1      MMA issuer:   one thread issues tcgen05.mma into one of two 256-column TMEM accumulators
+//   warps 2..5  epilogue:     drain the other accumulator (thread <-> TMEM lane <-> output row)
+// so that the epilogue of tile i overlaps the MMAs of tile i+1.
+//
+// Either operand may be K-major (K contiguous in global memory) or MN-major (M resp. N contiguous);
+// this is what lets the three contractions of the loss
+//   z  = x  * W        (A = x  K-major,  B = W  MN-major)      W is stored (H, V), V contiguous
+//   dx = dZ * W^T      (A = dZ K-major,  B = W  K-major)
+//   dW = x^T * dZ      (A = x  MN-major, B = dZ MN-major)
+// run from the same buffers without ever materialising a transpose.
+//
+// Shared-memory operand tiles use the 128-byte swizzle that TMA writes and UMMA descriptors read:
+//   K-major : row r (an M or N index) is 128 contiguous bytes of K at offset r * 128
+//             (8-row groups 1024 bytes apart = stride byte offset)
+//   MN-major: a TMA box is 128 bytes of MN x BLOCK_K rows of K (row k at offset k * 128; 8-row groups
+//             1024 bytes apart = stride byte offset); consecutive boxes along MN are BLOCK_K * 128 bytes
+//             apart (= leading byte offset). 32-bit MN-major operands use the 32-byte-atom variant of
+//             the swizzle (4-row groups, 512 bytes apart).
+#pragma once
+
+#include "ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace lce {
+
+enum : int { KIND_F16 = 0, KIND_BF16 = 1, KIND_TF32 = 2 };
+enum : int { EPI_F32 = 0, EPI_FWD = 1 };
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_N = 256;
+constexpr int kStages = 4;
+constexpr int kAccStages = 2;
+constexpr int kTmemCols = 512;
+constexpr int kGemmThreads = 192;
+constexpr int kATileBytes = BLOCK_M * 128;  // 16 KiB
+constexpr int kBTileBytes = BLOCK_N * 128;  // 32 KiB
+constexpr int kStageBytes = kATileBytes + kBTileBytes;
+
+// error codes written to the device status word
+enum : int { DEV_OK = 0, DEV_WAIT_TIMEOUT_PRODUCER = 101, DEV_WAIT_TIMEOUT_MMA = 102, DEV_WAIT_TIMEOUT_EPILOGUE = 103 };
+
+struct GemmShared {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full[kAccStages];
+  uint64_t acc_empty[kAccStages];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr size_t kGemmSmemBytes = size_t(kStages) * kStageBytes + 1024 /*alignment slack*/ + sizeof(GemmShared);
+
+struct GemmParams {
+  // tile grid; units = splits * n_tiles * m_tiles, m fastest
+  int m_tiles;
+  int n_tiles;
+  int splits;
+  int k_blocks;  // K-blocks (128 bytes of K each) per split
+  // element offsets added to the tensor-map coordinates
+  int a_mn0, a_k0, b_mn0, b_k0;
+
+  // ---- EPI_F32: plain fp32 tile store / read-add-store
+  float* out;
+  long long out_ld;            // elements between output rows
+  long long out_split_stride;  // elements between the outputs of consecutive K-splits
+  int accumulate;              // 0: out = coef * acc, 1: out += coef * acc
+  float out_scale;             // coef = out_scale / (*out_div)   (out_div may be null: coef = out_scale)
+  const float* out_div;
+
+  // ---- EPI_FWD: softmax statistics + exp slab
+  void* slab;                  // [rows, slab_ld] in the input element type: exp(z - tile row max)
+  long long slab_ld;
+  int store_slab;              // 0 when no gradient is wanted
+  float* tile_max;             // [n_tiles, stat_ld] per (V tile, row): max_j z
+  float* tile_sum;             //                    sum_j exp(z - max)
+  float* tile_ez;              //                    sum_j exp(z - max) * z      (monitoring)
+  float* tile_sq;              //                    sum_j z^2                  (monitoring)
+  long long stat_ld;
+  float* target_logit;         // [rows] z[i, y_i], written by the one tile that holds column y_i
+  const long long* labels;     // [rows]
+  long long ignore_index;
+  long long vocab_offset;      // global class id of local column 0
+  float scale;                 // logit scale (> 0)
+
+  int* status;                 // device status word (0 = ok)
+};
+
+// --------------------------------------------------------------------------------------------------
+// descriptors
+// --------------------------------------------------------------------------------------------------
+// Shared-memory matrix descriptor for a tile whose base is 1024-byte aligned.
+// 16-bit operands and K-major tf32 use the plain 128-byte swizzle (16-byte chunks permuted over 8 rows).
+// MN-major 32-bit operands exist in hardware only with the "128-byte swizzle, 32-byte atom" layout
+// (32-byte chunks permuted over 4 rows), so there the K rows come in groups of 4 (512 bytes).
+template <bool kMNMajor, int kBlockK, bool k32BitMN>
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  const uint64_t start = (smem_addr & 0x3FFFFu) >> 4;
+  const uint64_t lbo = kMNMajor ? uint64_t((kBlockK * 128) >> 4) : 1ull;  // MN-major: next 128-byte MN box
+  const uint64_t sbo = (k32BitMN ? 512ull : 1024ull) >> 4;                // next group of 8 (or 4) rows
+  const uint64_t layout = k32BitMN ? 1ull /*SWIZZLE_128B_BASE32B*/ : 2ull /*SWIZZLE_128B*/;
+  return start | (lbo << 16) | (sbo << 32) | (1ull << 46) /*descriptor version*/ | (layout << 61);
+}
+
+template <int kKind, bool kAMN, bool kBMN>
+__host__ __device__ constexpr uint32_t make_instr_desc() {
+  const uint32_t fmt = (kKind == KIND_F16) ? 0u : (kKind == KIND_BF16 ? 1u : 2u);
+  return (1u << 4)                         // D format: f32
+         | (fmt << 7) | (fmt << 10)        // A, B formats
+         | ((kAMN ? 1u : 0u) << 15)        // A major: 0 = K, 1 = MN
+         | ((kBMN ? 1u : 0u) << 16)        // B major
+         | (uint32_t(BLOCK_N >> 3) << 17)  // N
+         | (uint32_t(BLOCK_M >> 4) << 24); // M
+}
+
+// --------------------------------------------------------------------------------------------------
+// epilogues (one thread = one output row of the 128 x 256 tile)
+// --------------------------------------------------------------------------------------------------
+template <int kKind>
+struct SlabElem {
+  using type = __half;
+};
+template <>
+struct SlabElem<KIND_BF16> {
+  using type = __nv_bfloat16;
+};
+template <>
+struct SlabElem<KIND_TF32> {
+  using type = float;
+};
+
+__device__ __forceinline__ void store_slab_chunk(__half* dst, const float (&e)[32]) {
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __half2 h0 = __floats2half2_rn(e[8 * i + 0], e[8 * i + 1]);
+    __half2 h1 = __floats2half2_rn(e[8 * i + 2], e[8 * i + 3]);
+    __half2 h2 = __floats2half2_rn(e[8 * i + 4], e[8 * i + 5]);
+    __half2 h3 = __floats2half2_rn(e[8 * i + 6], e[8 * i + 7]);
+    uint4 v;
+    v.x = *reinterpret_cast<uint32_t*>(&h0);
+    v.y = *reinterpret_cast<uint32_t*>(&h1);
+    v.z = *reinterpret_cast<uint32_t*>(&h2);
+    v.w = *reinterpret_cast<uint32_t*>(&h3);
+    d4[i] = v;
+  }
+}
+__device__ __forceinline__ void store_slab_chunk(__nv_bfloat16* dst, const float (&e)[32]) {
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(e[8 * i + 0], e[8 * i + 1]);
+    __nv_bfloat162 h1 = __floats2bfloat162_rn(e[8 * i + 2], e[8 * i + 3]);
+    __nv_bfloat162 h2 = __floats2bfloat162_rn(e[8 * i + 4], e[8 * i + 5]);
+    __nv_bfloat162 h3 = __floats2bfloat162_rn(e[8 * i + 6], e[8 * i + 7]);
+    uint4 v;
+    v.x = *reinterpret_cast<uint32_t*>(&h0);
+    v.y = *reinterpret_cast<uint32_t*>(&h1);
+    v.z = *reinterpret_cast<uint32_t*>(&h2);
+    v.w = *reinterpret_cast<uint32_t*>(&h3);
+    d4[i] = v;
+  }
+}
+__device__ __forceinline__ void store_slab_chunk(float* dst, const float (&e)[32]) {
+  float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) d4[i] = make_float4(e[4 * i + 0], e[4 * i + 1], e[4 * i + 2], e[4 * i + 3]);
+}
+
+// Forward epilogue. For its row i and this tile's 256 columns j (z = scale * acc):
+//   tile_max = max_j z,  tile_sum = sum_j exp(z - tile_max),  slab[i, j] = exp(z - tile_max)
+//   target_logit[i] = z[i, y_i] if column y_i lies in this tile
+//   monitoring: tile_ez = sum_j exp(z - tile_max) * z,  tile_sq = sum_j z^2
+template <int kKind, bool kMonitor>
+__device__ __forceinline__ void epilogue_forward(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk,
+                                                 int row_in_tile) {
+  using Elem = typename SlabElem<kKind>::type;
+  const long long r = (long long)m_blk * BLOCK_M + row_in_tile;
+  const long long yv = p.labels[r];
+  const long long ycol_ll = yv - p.vocab_offset - (long long)n_blk * BLOCK_N;
+  const int ycol = (yv != p.ignore_index && ycol_ll >= 0 && ycol_ll < BLOCK_N) ? (int)ycol_ll : -1;
+
+  float mx = -INFINITY, sq = 0.f, tv = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < BLOCK_N / 32; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + c * 32, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float f = __uint_as_float(v[i]);
+      mx = fmaxf(mx, f);
+      if (kMonitor) sq = fmaf(f, f, sq);
+    }
+    if ((ycol >> 5) == c) {
+      const int sel = ycol & 31;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i == sel) tv = __uint_as_float(v[i]);
+    }
+  }
+
+  const float sl2 = p.scale * 1.4426950408889634f;  // scale * log2(e)
+  const float neg_m = -mx * sl2;
+  float s = 0.f, ez = 0.f;
+  Elem* slab_row = reinterpret_cast<Elem*>(p.slab) + r * p.slab_ld + (long long)n_blk * BLOCK_N;
+#pragma unroll 1
+  for (int c = 0; c < BLOCK_N / 32; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + c * 32, v);
+    tmem_ld_wait();
+    float e[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float f = __uint_as_float(v[i]);
+      e[i] = fast_exp2(fmaf(f, sl2, neg_m));
+      s += e[i];
+      if (kMonitor) ez = fmaf(e[i], f, ez);
+    }
+    if (p.store_slab) store_slab_chunk(slab_row + c * 32, e);
+  }
+
+  const long long si = (long long)n_blk * p.stat_ld + r;
+  p.tile_max[si] = mx * p.scale;
+  p.tile_sum[si] = s;
+  if (kMonitor) {
+    p.tile_ez[si] = ez * p.scale;
+    p.tile_sq[si] = sq * p.scale * p.scale;
+  }
+  if (ycol >= 0) p.target_logit[r] = tv * p.scale;
+}
+
+// Plain fp32 epilogue: out[split][row, col] (+)= coef * acc.
+__device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk, int split,
+                                             int row_in_tile) {
+  float* dst = p.out + (long long)split * p.out_split_stride +
+               ((long long)m_blk * BLOCK_M + row_in_tile) * p.out_ld + (long long)n_blk * BLOCK_N;
+  const float coef = (p.out_div != nullptr) ? p.out_scale / __ldg(p.out_div) : p.out_scale;
+#pragma unroll 1
+  for (int c = 0; c < BLOCK_N / 32; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + c * 32, v);
+    tmem_ld_wait();
+    float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
+    if (p.accumulate) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float4 o = d4[i];
+        o.x = fmaf(coef, __uint_as_float(v[4 * i + 0]), o.x);
+        o.y = fmaf(coef, __uint_as_float(v[4 * i + 1]), o.y);
+        o.z = fmaf(coef, __uint_as_float(v[4 * i + 2]), o.z);
+        o.w = fmaf(coef, __uint_as_float(v[4 * i + 3]), o.w);
+        d4[i] = o;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        d4[i] = make_float4(coef * __uint_as_float(v[4 * i + 0]), coef * __uint_as_float(v[4 * i + 1]),
+                            coef * __uint_as_float(v[4 * i + 2]), coef * __uint_as_float(v[4 * i + 3]));
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------------
+// the kernel
+// --------------------------------------------------------------------------------------------------
+template <int kKind, bool kAMN, bool kBMN, int kEpi, bool kMonitor>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const GemmParams p) {
+  constexpr int ES = (kKind == KIND_TF32) ? 4 : 2;  // operand element size in bytes
+  constexpr int BLOCK_K = 128 / ES;                 // elements of K per 128-byte swizzle row
+  constexpr int UMMA_K = 32 / ES;                   // K elements per tcgen05.mma
+  constexpr int MN_BOX = 128 / ES;                  // elements of MN per MN-major TMA box
+  constexpr int K_STEPS = BLOCK_K / UMMA_K;         // 4
+  // descriptor start-address advance (16-byte units) per UMMA_K step
+  constexpr uint32_t kAdvA = kAMN ? (UMMA_K * 128) >> 4 : 32 >> 4;
+  constexpr uint32_t kAdvB = kBMN ? (UMMA_K * 128) >> 4 : 32 >> 4;
+  constexpr uint32_t kIdesc = make_instr_desc<kKind, kAMN, kBMN>();
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  GemmShared* sh = reinterpret_cast<GemmShared*>(tiles + size_t(kStages) * kStageBytes);
+  volatile int* abort_flag = &sh->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], 1);
+    }
+    for (int a = 0; a < kAccStages; ++a) {
+      mbar_init(&sh->acc_full[a], 1);
+      mbar_init(&sh->acc_empty[a], 4);  // one arrival per epilogue warp
+    }
+    sh->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  const int units = p.splits * p.n_tiles * p.m_tiles;
+  const int tiles_mn = p.n_tiles * p.m_tiles;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
+        const int split = unit / tiles_mn;
+        const int rem = unit - split * tiles_mn;
+        const int n_blk = rem / p.m_tiles;
+        const int m_blk = rem - n_blk * p.m_tiles;
+        const int a_mn = p.a_mn0 + m_blk * BLOCK_M;
+        const int b_mn = p.b_mn0 + n_blk * BLOCK_N;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) {
+            atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          uint8_t* sA = tiles + size_t(stage) * kStageBytes;
+          uint8_t* sB = sA + kATileBytes;
+          const int kc = (split * p.k_blocks + kb) * BLOCK_K;
+          mbar_arrive_expect_tx(&sh->full[stage], kStageBytes);
+          if (!kAMN) {
+            tma_load_2d(sA, &tmA, &sh->full[stage], p.a_k0 + kc, a_mn);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_M / MN_BOX; ++j)
+              tma_load_2d(sA + j * (BLOCK_K * 128), &tmA, &sh->full[stage], a_mn + j * MN_BOX, p.a_k0 + kc);
+          }
+          if (!kBMN) {
+            tma_load_2d(sB, &tmB, &sh->full[stage], p.b_k0 + kc, b_mn);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_N / MN_BOX; ++j)
+              tma_load_2d(sB + j * (BLOCK_K * 128), &tmB, &sh->full[stage], b_mn + j * MN_BOX, p.b_k0 + kc);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
+        if (!mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
+          atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + uint32_t(acc * BLOCK_N);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&sh->full[stage], phase, abort_flag)) {
+            atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sA = smem_u32(tiles + size_t(stage) * kStageBytes);
+          const uint64_t adesc = make_smem_desc<kAMN, BLOCK_K, kAMN && kKind == KIND_TF32>(sA);
+          const uint64_t bdesc = make_smem_desc<kBMN, BLOCK_K, kBMN && kKind == KIND_TF32>(sA + kATileBytes);
+#pragma unroll
+          for (int k = 0; k < K_STEPS; ++k) {
+            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+            if (kKind == KIND_TF32)
+              umma_tf32(d_tmem, adesc + uint64_t(k * kAdvA), bdesc + uint64_t(k * kAdvB), kIdesc, accum);
+            else
+              umma_f16(d_tmem, adesc + uint64_t(k * kAdvA), bdesc + uint64_t(k * kAdvB), kIdesc, accum);
+          }
+          umma_commit(&sh->empty[stage]);  // frees the smem stage once these MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&sh->acc_full[acc]);  // accumulator complete -> epilogue
+        if (++acc == kAccStages) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int lane_group = warp & 3;  // a warp may only touch TMEM lanes [32 * (warp % 4), +32)
+    const int row_in_tile = lane_group * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+      const int split = unit / tiles_mn;
+      const int rem = unit - split * tiles_mn;
+      const int n_blk = rem / p.m_tiles;
+      const int m_blk = rem - n_blk * p.m_tiles;
+      if (!mbar_wait(&sh->acc_full[acc], acc_phase, abort_flag)) {
+        if (lane == 0) atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_EPILOGUE);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + uint32_t(acc * BLOCK_N);
+      if (kEpi == EPI_FWD)
+        epilogue_forward<kKind, kMonitor>(p, taddr, m_blk, n_blk, row_in_tile);
+      else
+        epilogue_f32(p, taddr, m_blk, n_blk, split, row_in_tile);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
+      if (++acc == kAccStages) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag != 0) {
+    // a wait ran out: give copies that may still be in flight time to land before smem goes away
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace lce

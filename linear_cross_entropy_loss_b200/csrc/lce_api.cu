@@ -1,0 +1,592 @@
+// C ABI of the library (declared in include/lce_b200.h): argument validation, workspace layout,
+// TMA tensor-map construction and kernel launches. No device memory is allocated here.
+#include "../../include/lce_b200.h"
+
+#include "aux_kernels.cuh"
+#include "gemm_sm100.cuh"
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+namespace {
+
+using namespace lce;
+
+std::atomic<long long> g_launches{0};
+
+// ------------------------------------------------------------------------------------------------
+// device bookkeeping
+// ------------------------------------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+std::mutex g_mutex;
+bool g_device_ready[kMaxDevices] = {};
+int g_device_sms[kMaxDevices] = {};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+template <int kKind, bool kAMN, bool kBMN, int kEpi, bool kMon>
+cudaError_t set_smem_attr() {
+  return cudaFuncSetAttribute(lce_gemm_kernel<kKind, kAMN, kBMN, kEpi, kMon>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes);
+}
+
+template <int kKind>
+cudaError_t set_smem_attr_kind() {
+  cudaError_t e;
+  if ((e = set_smem_attr<kKind, false, true, EPI_FWD, false>()) != cudaSuccess) return e;
+  if ((e = set_smem_attr<kKind, false, true, EPI_FWD, true>()) != cudaSuccess) return e;
+  if ((e = set_smem_attr<kKind, false, false, EPI_F32, false>()) != cudaSuccess) return e;
+  if ((e = set_smem_attr<kKind, true, true, EPI_F32, false>()) != cudaSuccess) return e;
+  if ((e = set_smem_attr<kKind, false, true, EPI_F32, false>()) != cudaSuccess) return e;
+  if ((e = set_smem_attr<kKind, true, false, EPI_F32, false>()) != cudaSuccess) return e;
+  return cudaSuccess;
+}
+
+// Once per device: check the architecture, raise the dynamic shared-memory limit of every GEMM
+// instantiation, fetch the tensor-map encoder from the driver. Returns the SM count through *sms.
+int ensure_device(int* sms) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return LCE_ERR_CUDA;
+  if (dev < 0 || dev >= kMaxDevices) return LCE_ERR_UNSUPPORTED_DEVICE;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_device_ready[dev]) {
+    int major = 0, count = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return LCE_ERR_CUDA;
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return LCE_ERR_CUDA;
+    if (major != 10) return LCE_ERR_UNSUPPORTED_DEVICE;
+    if (set_smem_attr_kind<KIND_F16>() != cudaSuccess) return LCE_ERR_CUDA;
+    if (set_smem_attr_kind<KIND_BF16>() != cudaSuccess) return LCE_ERR_CUDA;
+    if (set_smem_attr_kind<KIND_TF32>() != cudaSuccess) return LCE_ERR_CUDA;
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+          qres != cudaDriverEntryPointSuccess || fn == nullptr)
+        return LCE_ERR_DRIVER;
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    g_device_sms[dev] = count;
+    g_device_ready[dev] = true;
+  }
+  *sms = g_device_sms[dev];
+  return LCE_OK;
+}
+
+int sm_count_or_default() {
+  int dev = 0, count = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && count > 0)
+    return count;
+  return 148;  // B200
+}
+
+// ------------------------------------------------------------------------------------------------
+// shapes, workspace
+// ------------------------------------------------------------------------------------------------
+inline int elem_size(int dtype) { return dtype == LCE_DTYPE_F32 ? 4 : 2; }
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int validate_problem(const lce_problem* p) {
+  if (p == nullptr) return LCE_ERR_INVALID_ARGUMENT;
+  if (p->dtype != LCE_DTYPE_F16 && p->dtype != LCE_DTYPE_BF16 && p->dtype != LCE_DTYPE_F32)
+    return LCE_ERR_INVALID_ARGUMENT;
+  if (p->n_rows_total <= 0 || p->chunk_rows <= 0 || p->hidden <= 0 || p->vocab_local <= 0)
+    return LCE_ERR_INVALID_ARGUMENT;
+  if (p->world < 1 || p->vocab_offset < 0) return LCE_ERR_INVALID_ARGUMENT;
+  if (!(p->logit_scale > 0.f) || !(p->z_regularization >= 0.f)) return LCE_ERR_INVALID_ARGUMENT;
+  if (p->chunk_rows > p->n_rows_total) return LCE_ERR_INVALID_ARGUMENT;
+  if (p->n_rows_total % BLOCK_M != 0 || p->chunk_rows % BLOCK_M != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
+  if (p->hidden % 256 != 0 || p->vocab_local % 256 != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
+  // TMA coordinates and the kernels' tile counters are 32-bit
+  if (p->n_rows_total > (1ll << 30) || p->hidden > (1ll << 30) || p->vocab_local > (1ll << 30))
+    return LCE_ERR_TOO_LARGE;
+  return LCE_OK;
+}
+
+// K-split of the dx contraction (K = vocab_local): the smallest split whose work units fill the
+// SMs to >= 95 % in whole waves; the partials are reduced in a fixed order afterwards.
+int choose_dx_splits(const lce_problem* p, int sms) {
+  const long long tiles = (p->chunk_rows / BLOCK_M) * (p->hidden / BLOCK_N);
+  const long long kblocks = p->vocab_local * elem_size(p->dtype) / 128;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= 16; s *= 2) {
+    if (kblocks % s != 0 || kblocks / s < 8) break;
+    const long long units = tiles * s;
+    const long long waves = (units + sms - 1) / sms;
+    const double eff = (double)units / (double)(waves * sms);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = s;
+    }
+    if (eff >= 0.95) return s;
+  }
+  return best;
+}
+
+struct Workspace {
+  PassScalars* scalars;
+  float* tile_max;
+  float* tile_sum;
+  float* tile_ez;
+  float* tile_sq;
+  float* target_logit;
+  float* lse;
+  void* slab;
+  float* dx_part;
+  int dx_splits;
+  size_t total;
+};
+
+Workspace layout_workspace(const lce_problem* p, void* base, int sms) {
+  Workspace w;
+  const size_t n_tiles = (size_t)(p->vocab_local / BLOCK_N);
+  const size_t rows = (size_t)p->chunk_rows;
+  const size_t stat_bytes = align_up(n_tiles * rows * sizeof(float), 256);
+  char* b = reinterpret_cast<char*>(base);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    char* ptr = b + off;
+    off += align_up(bytes, 256);
+    return ptr;
+  };
+  w.scalars = reinterpret_cast<PassScalars*>(take(sizeof(PassScalars)));
+  w.tile_max = reinterpret_cast<float*>(take(stat_bytes));
+  w.tile_sum = reinterpret_cast<float*>(take(stat_bytes));
+  w.tile_ez = reinterpret_cast<float*>(take(p->monitoring ? stat_bytes : 0));
+  w.tile_sq = reinterpret_cast<float*>(take(p->monitoring ? stat_bytes : 0));
+  w.target_logit = reinterpret_cast<float*>(take(rows * sizeof(float)));
+  w.lse = reinterpret_cast<float*>(take(rows * sizeof(float)));
+  w.dx_splits = choose_dx_splits(p, sms);
+  if (p->want_grad) {
+    w.slab = take(rows * (size_t)p->vocab_local * elem_size(p->dtype));
+    w.dx_part = reinterpret_cast<float*>(take((size_t)w.dx_splits * rows * (size_t)p->hidden * sizeof(float)));
+  } else {
+    w.slab = nullptr;
+    w.dx_part = nullptr;
+  }
+  w.total = off;
+  return w;
+}
+
+// ------------------------------------------------------------------------------------------------
+// tensor maps
+// ------------------------------------------------------------------------------------------------
+// 2-D row-major tensor [outer, inner] (inner contiguous, rows `ld` elements apart), 128-byte swizzle.
+int make_tmap(CUtensorMap* map, int dtype, const void* base, long long inner, long long outer, long long ld,
+              int box_inner, int box_outer, bool atom32) {
+  const int es = elem_size(dtype);
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || ((ld * es) & 15) != 0) return LCE_ERR_MISALIGNED;
+  if (box_inner * es != 128 || box_outer > 256 || box_outer < 1) return LCE_ERR_INVALID_ARGUMENT;
+  const CUtensorMapDataType dt = dtype == LCE_DTYPE_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                 : dtype == LCE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  const cuuint64_t strides[1] = {(cuuint64_t)(ld * es)};
+  const cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LCE_OK : LCE_ERR_DRIVER;
+}
+
+// Operand tile boxes: K-major operand -> one box (128 bytes of K) x (tile rows);
+//                     MN-major operand -> boxes of (128 bytes of MN) x (BLOCK_K rows of K).
+int make_operand_tmap(CUtensorMap* map, int dtype, bool mn_major, const void* base, long long inner,
+                      long long outer, long long ld, int tile_mn) {
+  const int per128 = 128 / elem_size(dtype);
+  // MN-major 32-bit operands need the 32-byte-atom swizzle (see make_smem_desc)
+  return mn_major ? make_tmap(map, dtype, base, inner, outer, ld, per128, per128, dtype == LCE_DTYPE_F32)
+                  : make_tmap(map, dtype, base, inner, outer, ld, per128, tile_mn, false);
+}
+
+// ------------------------------------------------------------------------------------------------
+// launches
+// ------------------------------------------------------------------------------------------------
+int check_launch() {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
+}
+
+template <int kKind, bool kAMN, bool kBMN, int kEpi, bool kMon>
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& gp, int sms, cudaStream_t st) {
+  const long long units = (long long)gp.splits * gp.n_tiles * gp.m_tiles;
+  if (units <= 0 || units > (1ll << 30)) return LCE_ERR_TOO_LARGE;
+  const int grid = (int)(units < sms ? units : sms);
+  lce_gemm_kernel<kKind, kAMN, kBMN, kEpi, kMon><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(ta, tb, gp);
+  return check_launch();
+}
+
+template <bool kAMN, bool kBMN, int kEpi, bool kMon>
+int launch_gemm_dtype(int dtype, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& gp, int sms,
+                      cudaStream_t st) {
+  switch (dtype) {
+    case LCE_DTYPE_F16: return launch_gemm<KIND_F16, kAMN, kBMN, kEpi, kMon>(ta, tb, gp, sms, st);
+    case LCE_DTYPE_BF16: return launch_gemm<KIND_BF16, kAMN, kBMN, kEpi, kMon>(ta, tb, gp, sms, st);
+    case LCE_DTYPE_F32: return launch_gemm<KIND_TF32, kAMN, kBMN, kEpi, kMon>(ta, tb, gp, sms, st);
+  }
+  return LCE_ERR_INVALID_ARGUMENT;
+}
+
+int check_chunk(const lce_problem* p, int64_t row0, int64_t rows) {
+  if (row0 < 0 || rows <= 0 || rows > p->chunk_rows || row0 + rows > p->n_rows_total) return LCE_ERR_INVALID_ARGUMENT;
+  if (rows % BLOCK_M != 0 || row0 % BLOCK_M != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
+  return LCE_OK;
+}
+
+inline int grid_for(long long items, int per_block, int sms, int waves) {
+  long long g = (items + per_block - 1) / per_block;
+  const long long cap = (long long)sms * waves;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+}  // namespace
+
+// ================================================================================================
+// exported entry points
+// ================================================================================================
+extern "C" {
+
+int lce_version(void) { return 100; }
+
+const char* lce_status_string(int status) {
+  switch (status) {
+    case LCE_OK: return "ok";
+    case LCE_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case LCE_ERR_UNSUPPORTED_SHAPE:
+      return "unsupported shape (rows % 128, hidden % 256 and vocab % 256 must be 0)";
+    case LCE_ERR_MISALIGNED: return "pointer or row stride not 16-byte aligned";
+    case LCE_ERR_UNSUPPORTED_DEVICE: return "device is not compute capability 10.x (sm_100a required)";
+    case LCE_ERR_CUDA: return "CUDA runtime error";
+    case LCE_ERR_DEVICE_TIMEOUT: return "a bounded in-kernel wait ran out (device status word set)";
+    case LCE_ERR_DRIVER: return "driver call failed (cuTensorMapEncodeTiled)";
+    case LCE_ERR_TOO_LARGE: return "size exceeds the supported maximum";
+  }
+  return "unknown status";
+}
+
+long long lce_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int lce_workspace_bytes(const lce_problem* p, size_t* bytes) {
+  const int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if (bytes == nullptr) return LCE_ERR_INVALID_ARGUMENT;
+  *bytes = layout_workspace(p, nullptr, sm_count_or_default()).total;
+  return LCE_OK;
+}
+
+int lce_begin(const lce_problem* p, const int64_t* labels, void* workspace, void* stream) {
+  int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if (labels == nullptr || workspace == nullptr) return LCE_ERR_INVALID_ARGUMENT;
+  int sms = 0;
+  if ((v = ensure_device(&sms)) != LCE_OK) return v;
+  const Workspace w = layout_workspace(p, workspace, sms);
+  begin_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(reinterpret_cast<const long long*>(labels),
+                                                     (long long)p->n_rows_total, (long long)p->ignore_index,
+                                                     w.scalars);
+  return check_launch();
+}
+
+int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
+                      const int64_t* labels, int64_t row0, int64_t rows, void* workspace, float* row_parts_local,
+                      void* stream) {
+  int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if ((v = check_chunk(p, row0, rows)) != LCE_OK) return v;
+  if (!x || !weight || !labels || !workspace || !row_parts_local) return LCE_ERR_INVALID_ARGUMENT;
+  if (x_ld < p->hidden || w_ld < p->vocab_local) return LCE_ERR_INVALID_ARGUMENT;
+  int sms = 0;
+  if ((v = ensure_device(&sms)) != LCE_OK) return v;
+  cudaStream_t st = (cudaStream_t)stream;
+  const Workspace w = layout_workspace(p, workspace, sms);
+  const int es = elem_size(p->dtype);
+
+  CUtensorMap ta, tb;
+  if ((v = make_operand_tmap(&ta, p->dtype, false, x, p->hidden, p->n_rows_total, x_ld, BLOCK_M)) != LCE_OK) return v;
+  if ((v = make_operand_tmap(&tb, p->dtype, true, weight, p->vocab_local, p->hidden, w_ld, BLOCK_N)) != LCE_OK)
+    return v;
+
+  GemmParams gp;
+  memset(&gp, 0, sizeof(gp));
+  gp.m_tiles = (int)(rows / BLOCK_M);
+  gp.n_tiles = (int)(p->vocab_local / BLOCK_N);
+  gp.splits = 1;
+  gp.k_blocks = (int)(p->hidden * es / 128);
+  gp.a_mn0 = (int)row0;
+  gp.slab = w.slab;
+  gp.slab_ld = p->vocab_local;
+  gp.store_slab = (p->want_grad && w.slab != nullptr) ? 1 : 0;
+  gp.tile_max = w.tile_max;
+  gp.tile_sum = w.tile_sum;
+  gp.tile_ez = w.tile_ez;
+  gp.tile_sq = w.tile_sq;
+  gp.stat_ld = p->chunk_rows;
+  gp.target_logit = w.target_logit;
+  gp.labels = reinterpret_cast<const long long*>(labels) + row0;
+  gp.ignore_index = p->ignore_index;
+  gp.vocab_offset = p->vocab_offset;
+  gp.scale = p->logit_scale;
+  gp.status = &w.scalars->status;
+
+  v = p->monitoring ? launch_gemm_dtype<false, true, EPI_FWD, true>(p->dtype, ta, tb, gp, sms, st)
+                    : launch_gemm_dtype<false, true, EPI_FWD, false>(p->dtype, ta, tb, gp, sms, st);
+  if (v != LCE_OK) return v;
+
+  const int blocks = (int)((rows + 31) / 32);
+  const long long* lab = reinterpret_cast<const long long*>(labels) + row0;
+  if (p->monitoring)
+    row_stats_kernel<true><<<blocks, 256, 0, st>>>(w.tile_max, w.tile_sum, w.tile_ez, w.tile_sq, w.target_logit, lab,
+                                                   (int)rows, gp.n_tiles, p->chunk_rows, p->ignore_index,
+                                                   p->vocab_offset, p->vocab_local, row_parts_local);
+  else
+    row_stats_kernel<false><<<blocks, 256, 0, st>>>(w.tile_max, w.tile_sum, w.tile_ez, w.tile_sq, w.target_logit,
+                                                    lab, (int)rows, gp.n_tiles, p->chunk_rows, p->ignore_index,
+                                                    p->vocab_offset, p->vocab_local, row_parts_local);
+  return check_launch();
+}
+
+int lce_combine_chunk(const lce_problem* p, const float* row_parts_all, const int64_t* labels, int64_t row0,
+                      int64_t rows, void* workspace, void* stream) {
+  int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if ((v = check_chunk(p, row0, rows)) != LCE_OK) return v;
+  if (!row_parts_all || !labels || !workspace) return LCE_ERR_INVALID_ARGUMENT;
+  int sms = 0;
+  if ((v = ensure_device(&sms)) != LCE_OK) return v;
+  const Workspace w = layout_workspace(p, workspace, sms);
+  combine_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(row_parts_all, p->world,
+                                                       reinterpret_cast<const long long*>(labels) + row0, (int)rows,
+                                                       p->chunk_rows, p->ignore_index, p->monitoring, w.lse,
+                                                       w.scalars);
+  return check_launch();
+}
+
+int lce_backward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
+                       const int64_t* labels, int64_t row0, int64_t rows, void* workspace, void* dx, int64_t dx_ld,
+                       int32_t dx_dtype, float* dweight, int64_t dw_ld, int32_t first_chunk, void* stream) {
+  int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if ((v = check_chunk(p, row0, rows)) != LCE_OK) return v;
+  if (!p->want_grad) return LCE_ERR_INVALID_ARGUMENT;
+  if (!x || !weight || !labels || !workspace || !dx || !dweight) return LCE_ERR_INVALID_ARGUMENT;
+  if (x_ld < p->hidden || w_ld < p->vocab_local || dx_ld < p->hidden || dw_ld < p->vocab_local)
+    return LCE_ERR_INVALID_ARGUMENT;
+  if (dx_dtype != LCE_DTYPE_F16 && dx_dtype != LCE_DTYPE_BF16 && dx_dtype != LCE_DTYPE_F32)
+    return LCE_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(dweight) & 15u) != 0 || (dw_ld & 3) != 0) return LCE_ERR_MISALIGNED;
+  int sms = 0;
+  if ((v = ensure_device(&sms)) != LCE_OK) return v;
+  cudaStream_t st = (cudaStream_t)stream;
+  const Workspace w = layout_workspace(p, workspace, sms);
+  const int es = elem_size(p->dtype);
+  const int n_vtiles = (int)(p->vocab_local / BLOCK_N);
+  const long long* lab = reinterpret_cast<const long long*>(labels) + row0;
+
+  // ---- dZ, in place on the slab
+  {
+    const long long items = (rows / 8) * n_vtiles;
+    const int grid = grid_for(items, 1, sms, 16);
+    switch (p->dtype) {
+      case LCE_DTYPE_F16:
+        dz_transform_kernel<__half><<<grid, 256, 0, st>>>(reinterpret_cast<__half*>(w.slab), p->vocab_local,
+                                                          w.tile_max, w.lse, lab, (int)rows, n_vtiles, p->chunk_rows,
+                                                          p->ignore_index, p->vocab_offset, p->z_regularization);
+        break;
+      case LCE_DTYPE_BF16:
+        dz_transform_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+            reinterpret_cast<__nv_bfloat16*>(w.slab), p->vocab_local, w.tile_max, w.lse, lab, (int)rows, n_vtiles,
+            p->chunk_rows, p->ignore_index, p->vocab_offset, p->z_regularization);
+        break;
+      default:
+        dz_transform_kernel<float><<<grid, 256, 0, st>>>(reinterpret_cast<float*>(w.slab), p->vocab_local,
+                                                         w.tile_max, w.lse, lab, (int)rows, n_vtiles, p->chunk_rows,
+                                                         p->ignore_index, p->vocab_offset, p->z_regularization);
+    }
+    if ((v = check_launch()) != LCE_OK) return v;
+  }
+
+  CUtensorMap ta, tb;
+  // ---- dx partials = dZ * W^T over K-splits of the vocabulary, scaled by logit_scale / n_valid
+  {
+    if ((v = make_operand_tmap(&ta, p->dtype, false, w.slab, p->vocab_local, p->chunk_rows, p->vocab_local,
+                               BLOCK_M)) != LCE_OK)
+      return v;
+    if ((v = make_operand_tmap(&tb, p->dtype, false, weight, p->vocab_local, p->hidden, w_ld, BLOCK_N)) != LCE_OK)
+      return v;
+    GemmParams gp;
+    memset(&gp, 0, sizeof(gp));
+    gp.m_tiles = (int)(rows / BLOCK_M);
+    gp.n_tiles = (int)(p->hidden / BLOCK_N);
+    gp.splits = w.dx_splits;
+    gp.k_blocks = (int)(p->vocab_local * es / 128 / w.dx_splits);
+    gp.out = w.dx_part;
+    gp.out_ld = p->hidden;
+    gp.out_split_stride = (long long)p->chunk_rows * p->hidden;
+    gp.accumulate = 0;
+    gp.out_scale = p->logit_scale;
+    gp.out_div = &w.scalars->n_valid;
+    gp.status = &w.scalars->status;
+    if ((v = launch_gemm_dtype<false, false, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st)) != LCE_OK) return v;
+
+    const long long quads = rows * (p->hidden / 4);
+    const int grid = grid_for(quads, 256, sms, 8);
+    const long long ss = (long long)p->chunk_rows * p->hidden;
+    char* dx_rows = reinterpret_cast<char*>(dx) + (size_t)row0 * (size_t)dx_ld * elem_size(dx_dtype);
+    switch (dx_dtype) {
+      case LCE_DTYPE_F16:
+        dx_reduce_kernel<__half><<<grid, 256, 0, st>>>(w.dx_part, w.dx_splits, ss, (int)rows, (int)p->hidden,
+                                                       reinterpret_cast<__half*>(dx_rows), dx_ld);
+        break;
+      case LCE_DTYPE_BF16:
+        dx_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(w.dx_part, w.dx_splits, ss, (int)rows, (int)p->hidden,
+                                                              reinterpret_cast<__nv_bfloat16*>(dx_rows), dx_ld);
+        break;
+      default:
+        dx_reduce_kernel<float><<<grid, 256, 0, st>>>(w.dx_part, w.dx_splits, ss, (int)rows, (int)p->hidden,
+                                                      reinterpret_cast<float*>(dx_rows), dx_ld);
+    }
+    if ((v = check_launch()) != LCE_OK) return v;
+  }
+
+  // ---- dW (+)= x^T * dZ, scaled by logit_scale / n_valid
+  {
+    if ((v = make_operand_tmap(&ta, p->dtype, true, x, p->hidden, p->n_rows_total, x_ld, BLOCK_M)) != LCE_OK)
+      return v;
+    if ((v = make_operand_tmap(&tb, p->dtype, true, w.slab, p->vocab_local, p->chunk_rows, p->vocab_local,
+                               BLOCK_N)) != LCE_OK)
+      return v;
+    GemmParams gp;
+    memset(&gp, 0, sizeof(gp));
+    gp.m_tiles = (int)(p->hidden / BLOCK_M);
+    gp.n_tiles = n_vtiles;
+    gp.splits = 1;
+    gp.k_blocks = (int)(rows * es / 128);
+    gp.a_k0 = (int)row0;
+    gp.out = dweight;
+    gp.out_ld = dw_ld;
+    gp.out_split_stride = 0;
+    gp.accumulate = first_chunk ? 0 : 1;
+    gp.out_scale = p->logit_scale;
+    gp.out_div = &w.scalars->n_valid;
+    gp.status = &w.scalars->status;
+    if ((v = launch_gemm_dtype<true, true, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st)) != LCE_OK) return v;
+  }
+  return LCE_OK;
+}
+
+int lce_finalize(const lce_problem* p, void* workspace, float* out5, void* stream) {
+  int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if (!workspace || !out5) return LCE_ERR_INVALID_ARGUMENT;
+  int sms = 0;
+  if ((v = ensure_device(&sms)) != LCE_OK) return v;
+  const Workspace w = layout_workspace(p, workspace, sms);
+  finalize_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(w.scalars, (double)p->n_rows_total, p->z_regularization, out5);
+  return check_launch();
+}
+
+}  // extern "C"
+
+namespace {
+template <typename S>
+int scale_cast_dst(const S* src, long long src_ld, void* dst, int dst_dtype, long long dst_ld, long long rows,
+                   long long cols, const float* f, int grid, cudaStream_t st) {
+  switch (dst_dtype) {
+    case LCE_DTYPE_F16:
+      scale_cast_kernel<S, __half><<<grid, 256, 0, st>>>(src, src_ld, reinterpret_cast<__half*>(dst), dst_ld, rows,
+                                                         cols, f);
+      break;
+    case LCE_DTYPE_BF16:
+      scale_cast_kernel<S, __nv_bfloat16><<<grid, 256, 0, st>>>(src, src_ld, reinterpret_cast<__nv_bfloat16*>(dst),
+                                                                dst_ld, rows, cols, f);
+      break;
+    case LCE_DTYPE_F32:
+      scale_cast_kernel<S, float><<<grid, 256, 0, st>>>(src, src_ld, reinterpret_cast<float*>(dst), dst_ld, rows,
+                                                        cols, f);
+      break;
+    default: return LCE_ERR_INVALID_ARGUMENT;
+  }
+  return check_launch();
+}
+}  // namespace
+
+extern "C" {
+
+int lce_grad_scale_cast(const void* src, int32_t src_dtype, int64_t src_ld, void* dst, int32_t dst_dtype,
+                        int64_t dst_ld, int64_t rows, int64_t cols, const float* dev_factor, void* stream) {
+  if (!src || !dst || !dev_factor || rows <= 0 || cols <= 0 || src_ld < cols || dst_ld < cols)
+    return LCE_ERR_INVALID_ARGUMENT;
+  const int sms = sm_count_or_default();
+  const int grid = grid_for(rows * cols, 256 * 4, sms, 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (src_dtype) {
+    case LCE_DTYPE_F16:
+      return scale_cast_dst(reinterpret_cast<const __half*>(src), src_ld, dst, dst_dtype, dst_ld, rows, cols,
+                            dev_factor, grid, st);
+    case LCE_DTYPE_BF16:
+      return scale_cast_dst(reinterpret_cast<const __nv_bfloat16*>(src), src_ld, dst, dst_dtype, dst_ld, rows, cols,
+                            dev_factor, grid, st);
+    case LCE_DTYPE_F32:
+      return scale_cast_dst(reinterpret_cast<const float*>(src), src_ld, dst, dst_dtype, dst_ld, rows, cols,
+                            dev_factor, grid, st);
+  }
+  return LCE_ERR_INVALID_ARGUMENT;
+}
+
+int lce_read_status(void* workspace, void* stream) {
+  if (!workspace) return LCE_ERR_INVALID_ARGUMENT;
+  PassScalars host;
+  if (cudaMemcpyAsync(&host, workspace, sizeof(host), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess)
+    return LCE_ERR_CUDA;
+  if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return LCE_ERR_CUDA;
+  return host.status == 0 ? LCE_OK : LCE_ERR_DEVICE_TIMEOUT;
+}
+
+int lce_debug_gemm(int32_t dtype, int32_t a_mn_major, int32_t b_mn_major, const void* a, int64_t a_ld, const void* b,
+                   int64_t b_ld, float* out, int64_t m, int64_t n, int64_t k, int32_t splits, int* dev_status,
+                   void* stream) {
+  if (dtype != LCE_DTYPE_F16 && dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F32) return LCE_ERR_INVALID_ARGUMENT;
+  if (!a || !b || !out || !dev_status || m <= 0 || n <= 0 || k <= 0 || splits < 1) return LCE_ERR_INVALID_ARGUMENT;
+  const int es = elem_size(dtype);
+  const int bk = 128 / es;
+  if (m % BLOCK_M != 0 || n % BLOCK_N != 0 || k % ((long long)bk * splits) != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
+  if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) return LCE_ERR_TOO_LARGE;
+  int sms = 0;
+  int v = ensure_device(&sms);
+  if (v != LCE_OK) return v;
+  CUtensorMap ta, tb;
+  v = a_mn_major ? make_operand_tmap(&ta, dtype, true, a, m, k, a_ld, BLOCK_M)
+                 : make_operand_tmap(&ta, dtype, false, a, k, m, a_ld, BLOCK_M);
+  if (v != LCE_OK) return v;
+  v = b_mn_major ? make_operand_tmap(&tb, dtype, true, b, n, k, b_ld, BLOCK_N)
+                 : make_operand_tmap(&tb, dtype, false, b, k, n, b_ld, BLOCK_N);
+  if (v != LCE_OK) return v;
+  GemmParams gp;
+  memset(&gp, 0, sizeof(gp));
+  gp.m_tiles = (int)(m / BLOCK_M);
+  gp.n_tiles = (int)(n / BLOCK_N);
+  gp.splits = splits;
+  gp.k_blocks = (int)(k / bk / splits);
+  gp.out = out;
+  gp.out_ld = n;
+  gp.out_split_stride = m * n;
+  gp.out_scale = 1.f;
+  gp.status = dev_status;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!a_mn_major && !b_mn_major) return launch_gemm_dtype<false, false, EPI_F32, false>(dtype, ta, tb, gp, sms, st);
+  if (!a_mn_major && b_mn_major) return launch_gemm_dtype<false, true, EPI_F32, false>(dtype, ta, tb, gp, sms, st);
+  if (a_mn_major && !b_mn_major) return launch_gemm_dtype<true, false, EPI_F32, false>(dtype, ta, tb, gp, sms, st);
+  return launch_gemm_dtype<true, true, EPI_F32, false>(dtype, ta, tb, gp, sms, st);
+}
+
+}  // extern "C"

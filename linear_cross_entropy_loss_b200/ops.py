@@ -1,0 +1,350 @@
+"""Fused linear + cross-entropy loss on B200: the reference's Python surface over the C ABI.
+
+Mirrors ``linear_cross_entropy/ops.py`` of JonasGeiping/linear_cross_entropy_loss:
+
+* ``LinearXentImplementation`` (ops.py:661-810 there): an ``autograd.Function`` that computes the loss
+  AND both gradients during ``forward`` -- chunk by chunk over the rows, so that at most one
+  ``N_chunk_size x V`` slab is live -- and only rescales them by ``grad_output`` in ``backward``.
+* ``linear_cross_entropy`` (ops.py:814-826): functional form returning the 5-tuple
+  ``(loss, z_value, logit_max, logit_entropy, logit_norm)``.
+* ``LinearCrossEntropyLoss`` (ops.py:830-955): ``nn.Linear`` subclass whose weight is stored
+  transposed, ``(in_features, out_features)``.
+
+Everything numeric happens in ``liblce_b200.so`` (hand-written sm_100a kernels); this file only owns
+device memory, streams and the chunk loop. There is no CPU or eager fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+
+from . import _native
+from ._native import DTYPE_BF16, DTYPE_F16, DTYPE_F32, ROW_PARTS, Problem
+
+# The reference exports its Triton autotune lists under these names (linear_cross_entropy/__init__.py:1)
+# so that users can trim them. There is nothing to autotune here; the names stay importable.
+fwd_configs: list = []
+bwd_configs: list = []
+
+_DTYPE_CODE = {torch.float16: DTYPE_F16, torch.bfloat16: DTYPE_BF16, torch.float32: DTYPE_F32}
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class NativeBackend:
+    """Calls into liblce_b200.so on the current CUDA stream of the tensors' device."""
+
+    name = "liblce_b200"
+
+    def __init__(self):
+        self.lib = _native.load()
+
+    @staticmethod
+    def _stream(t: torch.Tensor) -> int:
+        return torch.cuda.current_stream(t.device).cuda_stream
+
+    def workspace_bytes(self, prob: Problem) -> int:
+        out = ctypes.c_size_t(0)
+        _native.check(self.lib.lce_workspace_bytes(ctypes.byref(prob), ctypes.byref(out)), "lce_workspace_bytes")
+        return int(out.value)
+
+    def begin(self, prob, y, workspace):
+        _native.check(
+            self.lib.lce_begin(ctypes.byref(prob), _ptr(y), _ptr(workspace), self._stream(workspace)), "lce_begin"
+        )
+
+    def forward_chunk(self, prob, x, At, y, row0, rows, workspace, row_parts):
+        _native.check(
+            self.lib.lce_forward_chunk(
+                ctypes.byref(prob), _ptr(x), x.stride(0), _ptr(At), At.stride(0), _ptr(y), row0, rows,
+                _ptr(workspace), _ptr(row_parts), self._stream(workspace),
+            ),
+            "lce_forward_chunk",
+        )
+
+    def combine_chunk(self, prob, row_parts_all, y, row0, rows, workspace):
+        _native.check(
+            self.lib.lce_combine_chunk(
+                ctypes.byref(prob), _ptr(row_parts_all), _ptr(y), row0, rows, _ptr(workspace), self._stream(workspace)
+            ),
+            "lce_combine_chunk",
+        )
+
+    def backward_chunk(self, prob, x, At, y, row0, rows, workspace, dx, dA, first_chunk):
+        _native.check(
+            self.lib.lce_backward_chunk(
+                ctypes.byref(prob), _ptr(x), x.stride(0), _ptr(At), At.stride(0), _ptr(y), row0, rows,
+                _ptr(workspace), _ptr(dx), dx.stride(0), _DTYPE_CODE[dx.dtype], _ptr(dA), dA.stride(0),
+                1 if first_chunk else 0, self._stream(workspace),
+            ),
+            "lce_backward_chunk",
+        )
+
+    def finalize(self, prob, workspace, out5):
+        _native.check(
+            self.lib.lce_finalize(ctypes.byref(prob), _ptr(workspace), _ptr(out5), self._stream(workspace)),
+            "lce_finalize",
+        )
+
+    def grad_scale_cast(self, src, dst, factor):
+        _native.check(
+            self.lib.lce_grad_scale_cast(
+                _ptr(src), _DTYPE_CODE[src.dtype], src.stride(0), _ptr(dst), _DTYPE_CODE[dst.dtype], dst.stride(0),
+                src.shape[0], src.shape[1], _ptr(factor), self._stream(src),
+            ),
+            "lce_grad_scale_cast",
+        )
+
+    def read_status(self, workspace) -> int:
+        return int(self.lib.lce_read_status(_ptr(workspace), self._stream(workspace)))
+
+
+_backend = None
+
+
+def get_backend():
+    """The object the chunk loop drives. Always the native library outside of unit tests."""
+    global _backend
+    if _backend is None:
+        _backend = NativeBackend()
+    return _backend
+
+
+def set_backend(backend) -> None:
+    """Test hook: substitute the object that receives the per-chunk calls (None restores the library)."""
+    global _backend
+    _backend = backend
+
+
+@dataclass
+class ShardSpec:
+    """Vocabulary sharding of W over the ranks of a process group (None = the whole W is local).
+
+    gather_row_parts(local[ROW_PARTS * chunk_rows]) -> all[world * ROW_PARTS * chunk_rows] (rank-major)
+    reduce_dx(dx_rows) sums the chunk's dx rows over the ranks, in place.
+    """
+
+    rank: int
+    world: int
+    vocab_offset: int
+    gather_row_parts: Callable[[torch.Tensor], torch.Tensor]
+    reduce_dx: Callable[[torch.Tensor], None]
+
+
+def grad_buffer_dtype(dtype: torch.dtype) -> torch.dtype:
+    """dx is kept in fp32 for bf16 inputs and in the input type otherwise (reference ops.py:693-694)."""
+    return torch.float32 if dtype == torch.bfloat16 else dtype
+
+
+def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size, monitoring, want_grad,
+             shard: Optional[ShardSpec] = None):
+    """One forward(+gradient) pass over all row chunks.
+
+    x: (N, H) with unit inner stride, y: (N,) int64 contiguous, At: (H, V_local) with unit inner stride.
+    Returns (out5, dx, dA, workspace): out5 = float32[5] (loss, z_value, logit_max, logit_entropy,
+    logit_norm); dx (N, H) in grad_buffer_dtype(x.dtype) and dA (H, V_local) float32, or None without
+    want_grad. Follows the chunk loop of the reference (ops.py:721-791).
+    """
+    backend = get_backend()
+    N, H = x.shape
+    H_A, V = At.shape
+    assert H_A == H, "x and the weight disagree on the hidden size"
+    assert y.shape == (N,), "labels must have one entry per row of x"
+    assert x.dtype == At.dtype, "x and the weight must have the same dtype"
+    assert x.dtype in _DTYPE_CODE, f"unsupported dtype {x.dtype}"
+    assert y.dtype == torch.int64, "labels must be int64"
+    assert N % 128 == 0, "the number of rows (B*S) must be divisible by 128"
+    assert V % 256 == 0, "the (local) vocabulary size must be divisible by 256"
+    assert H % 256 == 0, "the hidden size must be divisible by 256"
+    assert logit_scale > 0 and z_regularization >= 0
+    N_group = min(N, int(N_chunk_size))
+    assert N_group % 128 == 0, "N_chunk_size must be divisible by 128"
+
+    world = 1 if shard is None else shard.world
+    prob = Problem(
+        n_rows_total=N, chunk_rows=N_group, hidden=H, vocab_local=V,
+        vocab_offset=0 if shard is None else shard.vocab_offset, ignore_index=int(ignore_index), world=world,
+        dtype=_DTYPE_CODE[x.dtype], monitoring=1 if monitoring else 0, want_grad=1 if want_grad else 0,
+        logit_scale=float(logit_scale), z_regularization=float(z_regularization),
+    )
+    dev = x.device
+    workspace = torch.empty(backend.workspace_bytes(prob), dtype=torch.uint8, device=dev)
+    row_parts = torch.empty(ROW_PARTS * N_group, dtype=torch.float32, device=dev)
+    out5 = torch.empty(5, dtype=torch.float32, device=dev)
+    dx = dA = None
+    if want_grad:
+        dx = torch.empty((N, H), dtype=grad_buffer_dtype(x.dtype), device=dev)
+        dA = torch.empty((H, V), dtype=torch.float32, device=dev)
+
+    backend.begin(prob, y, workspace)
+    first = True
+    for row0 in range(0, N, N_group):
+        rows = min(N_group, N - row0)
+        backend.forward_chunk(prob, x, At, y, row0, rows, workspace, row_parts)
+        parts_all = row_parts if shard is None else shard.gather_row_parts(row_parts)
+        backend.combine_chunk(prob, parts_all, y, row0, rows, workspace)
+        if want_grad:
+            backend.backward_chunk(prob, x, At, y, row0, rows, workspace, dx, dA, first)
+            if shard is not None:
+                shard.reduce_dx(dx[row0:row0 + rows])
+        first = False
+    backend.finalize(prob, workspace, out5)
+    return out5, dx, dA, workspace
+
+
+def _prepare(x_in, y, At):
+    x = x_in.reshape(-1, x_in.shape[-1])
+    if x.stride(-1) != 1 or (x.stride(0) * x.element_size()) % 16 != 0:
+        x = x.contiguous()
+    y = y.reshape(-1)
+    if not y.is_contiguous():
+        y = y.contiguous()
+    if At.stride(-1) != 1 or (At.stride(0) * At.element_size()) % 16 != 0:
+        At = At.contiguous()
+    return x, y, At
+
+
+def _scaled_grads(ctx, grad_output):
+    """grad * grad_output in the dtype of the corresponding input (reference ops.py:804-810)."""
+    backend = get_backend()
+    dx, dA = ctx.lce_grads
+    ctx.lce_grads = None
+    factor = grad_output.detach().reshape(1).to(device=dx.device, dtype=torch.float32).contiguous()
+    x_dtype, a_dtype = ctx.lce_dtypes
+    gx = dx if dx.dtype == x_dtype else torch.empty(dx.shape, dtype=x_dtype, device=dx.device)
+    backend.grad_scale_cast(dx, gx, factor)
+    gA = dA if dA.dtype == a_dtype else torch.empty(dA.shape, dtype=a_dtype, device=dA.device)
+    backend.grad_scale_cast(dA, gA, factor)
+    return gx.view(ctx.lce_x_shape), gA
+
+
+class LinearXentImplementation(torch.autograd.Function):
+    """Same call signature and outputs as the reference's autograd function (ops.py:661-810)."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float16)
+    def forward(ctx, x_in, y, At, ignore_index=-100, z_regularization: float = 0.0, logit_scale: float = 1.0,
+                N_chunk_size: int = 4096, monitoring: bool = True):
+        # Under CUDA autocast the decorator casts floating inputs to fp16 and disables autocast
+        # inside, exactly as the reference does (ops.py:665-667).
+        with torch.cuda.device(x_in.device):
+            x, y_flat, A = _prepare(x_in, y, At)
+            want_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[2])
+            with torch.no_grad():
+                out5, dx, dA, _ = run_pass(x, y_flat, A, ignore_index, z_regularization, logit_scale, N_chunk_size,
+                                           monitoring, want_grad)
+            ctx.lce_grads = (dx, dA) if want_grad else None
+            ctx.lce_dtypes = (x_in.dtype, At.dtype)
+            ctx.lce_x_shape = x_in.shape
+            loss, z_value, logit_max, logit_ent, logit_norm = out5.unbind(0)
+            ctx.mark_non_differentiable(z_value, logit_max, logit_ent, logit_norm)
+            return loss, z_value, logit_max, logit_ent, logit_norm
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, grad_output, void0, void1, void2, void3):
+        if ctx.lce_grads is None:
+            raise RuntimeError("backward called twice, or forward ran without any input requiring grad")
+        with torch.cuda.device(grad_output.device), torch.no_grad():
+            gx, gA = _scaled_grads(ctx, grad_output)
+        return gx, None, gA, None, None, None, None, None
+
+
+def linear_cross_entropy(
+    x,
+    y,
+    At,
+    ignore_index=-100,
+    z_regularization: float = 0.0,
+    logit_scale: float = 1.0,
+    N_chunk_size: int = 4096,
+    monitoring: bool = False,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Functional form (reference ops.py:814-826): returns (loss, z_value, logit_max, logit_entropy, logit_norm)."""
+    return LinearXentImplementation.apply(
+        x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size, monitoring
+    )  # type: ignore
+
+
+class LinearCrossEntropyLoss(torch.nn.Linear):
+    r"""``z = x @ weight`` followed at once by the cross-entropy of ``z`` with labels ``y``; returns the scalar loss.
+
+    Drop-in for the reference module (ops.py:830-955): same constructor, attributes and ``state_dict``
+    (one key, ``weight``, of shape ``(in_features, out_features)`` -- transposed with respect to
+    ``nn.Linear``; there is no bias). It subclasses ``nn.Linear`` so that code which looks for linear
+    layers (initialisation, weight decay groups) finds it.
+
+    Setting ``module.monitoring = True`` makes ``forward`` also fill ``module.latest_metrics`` with
+    ``logit_norm``, ``logit_max``, ``logit_entropy`` and ``z_value``, defined as in the reference's
+    ``reference_torch`` (ops.py:9-17).
+
+    Differences from the reference, all of them relaxations: shapes need only N % 128, H % 256 and
+    V % 256 (the reference needs N % 512, H % 256, V % 4096), there is no autotuning on the first call,
+    and gradients are only computed when an input requires them.
+    """
+
+    def __init__(
+        self,
+        in_features: int,
+        out_features: int,
+        device=None,
+        dtype=None,
+        ignore_index: int = -100,
+        logit_scale: float = 1.0,
+        z_regularization: float = 0.0,
+        N_chunk_size: int = 4096,
+        init_method=None,
+    ):
+        factory_kwargs = {"device": device, "dtype": dtype}
+        torch.nn.Module.__init__(self)  # not nn.Linear.__init__: no bias, transposed weight
+
+        assert in_features % 256 == 0
+        assert out_features % 256 == 0
+        assert N_chunk_size % 128 == 0
+        assert logit_scale > 0
+        assert z_regularization >= 0
+
+        self.in_features = in_features
+        self.out_features = out_features
+        self.weight = torch.nn.Parameter(torch.empty((in_features, out_features), **factory_kwargs))
+
+        self.logit_scale = logit_scale
+        self.ignore_index = ignore_index
+        self.z_regularization = z_regularization
+        self.N_chunk_size = N_chunk_size
+
+        self.monitoring = False
+        self.latest_metrics = {}
+        self.init_method = init_method
+
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        if self.init_method is not None:
+            self.init_method(self.weight)
+        else:
+            std = math.sqrt(1 / self.in_features)
+            torch.nn.init.trunc_normal_(self.weight, mean=0.0, std=std, a=-3 * std, b=3 * std)
+
+    def forward(self, x, y):
+        loss, z_reg, logit_max, logit_ent, logit_norm = LinearXentImplementation.apply(
+            x, y, self.weight, self.ignore_index, self.z_regularization, self.logit_scale, self.N_chunk_size,
+            self.monitoring,
+        )  # type: ignore
+        if self.monitoring:
+            self.latest_metrics = {
+                "logit_norm": logit_norm,
+                "logit_max": logit_max,
+                "logit_entropy": logit_ent,
+                "z_value": z_reg,
+            }
+        return loss
+
+    def extra_repr(self) -> str:
+        return f"in_features={self.in_features}, out_features={self.out_features}, bias=False"
