@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Benchmark of the fused linear + cross-entropy path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config NAME] [--scaling weak|strong]
+
+A step is one forward+backward of ``linear_cross_entropy`` over one batch of synthetic inputs (loss, dx and dW),
+the quantity the reference's own benchmark times (bench_fusions.py:261-266 of the reference). The metric is the
+reference's: fwd+bwd TFLOP/s = 6*N*H*V / t. One JSON line is printed by rank 0.
+
+N = 1: the default point of the reference's sweeps in bf16 (N=16384, H=2048, V=131072, N_chunk_size=4096).
+N > 1 (launched by torch.distributed.run, one rank per GPU): the weight is sharded by vocabulary columns over the
+ranks (linear_cross_entropy_loss_b200/sharded.py). ``--scaling weak`` (default) keeps one 131072-column slab per
+rank, so the global vocabulary is N_gpus * 131072; ``--scaling strong`` shards the named configuration itself.
+
+``--impl reference`` times the reference's torch statement of the path (float32, CPU, all host threads) through
+the oracle's port of it on a bounded sample of the same workload; rank 0 only.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "fwd+bwd TFLOP/s (6NHV/t)"
+# published number for this metric at the default point in bf16 (fused Triton kernel, unknown 48 GB GPU):
+# reference file "bench/bf16 fwd-bwd-Linear+Loss Performance over N. ...csv", line 8
+PUBLISHED_BF16_DEFAULT_TFLOPS = 86.75
+# fallback roofline denominators when the measured-peaks file is absent (earlier measurement on this pool)
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+# DRAM bytes (read + write) of ONE launch of each contraction kernel at the headline shape, from the ncu captures
+# summarised under profiles/ (null until captured)
+NCU_DRAM_BYTES_PER_LAUNCH = {"fwd": None, "dx": None, "dw": None}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--config", default="headline_bf16")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1, rank 0)")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU work of the baseline leg")
+    ap.add_argument("--ref-budget", type=float, default=100.0,
+                    help="--impl reference: seconds of CPU work over all warm-up and timed steps together")
+    return ap.parse_args()
+
+
+def load_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()), "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ---------------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        ids = [v.strip() for v in vis.split(",") if v.strip()]
+        if local_rank < len(ids) and ids[local_rank].isdigit():
+            return int(ids[local_rank])
+    return local_rank
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU legs (the reference's torch path, ported in oracle/oracle.py)
+# ---------------------------------------------------------------------------------------------------
+def cpu_reference_rate(cfg, seconds, steps=1, warmup=0):
+    """Times oracle.cpu_baseline_step on a bounded row/column sample of cfg. Returns (tflops, ms_per_step, info)."""
+    import torch
+
+    from oracle import oracle
+
+    torch.manual_seed(0)
+    cores = torch.get_num_threads()
+    V = min(cfg.V, 131072)
+    H = cfg.H
+    g = torch.Generator().manual_seed(cfg.seed)
+    W = torch.randn(H, V, generator=g).clamp_(-2, 2).mul_(H ** -0.5)
+
+    def run(rows):
+        x = torch.randn(rows, H, generator=g)
+        y = torch.randint(0, V, (rows,), generator=g)
+        y[torch.rand(rows, generator=g) < cfg.frac_ignored] = cfg.ignore_index
+        t0 = time.perf_counter()
+        oracle.cpu_baseline_step(x, y, W, cfg.ignore_index, cfg.z_regularization, cfg.logit_scale,
+                                 chunk_rows=min(rows, 1024))
+        return time.perf_counter() - t0
+
+    run(128)                                   # touches the pages, spins up the thread pool
+    t = run(128)
+    rate = 6.0 * 128 * H * V / t               # flop/s estimate
+    rows = int(seconds * rate / (6.0 * H * V)) // 128 * 128
+    rows = max(128, min(rows, cfg.N))
+    for _ in range(warmup):
+        run(rows)
+    times = [run(rows) for _ in range(max(1, steps))]
+    t = sum(times) / len(times)
+    tflops = 6.0 * rows * H * V / t / 1e12
+    info = {"kind": "port", "cores": cores, "value": tflops, "unit": "TFLOP/s",
+            "sample": f"{rows} of {cfg.N} rows x H={H} x {V} of {cfg.V} vocabulary columns per step, float32, "
+                      f"torch CPU F.linear + F.cross_entropy + autograd (the reference's reference_torch), "
+                      f"{len(times)} timed step(s)"}
+    return tflops, t * 1e3, info
+
+
+def run_reference_arm(args, cfg, n_gpus):
+    per_step = max(0.25, args.ref_budget / max(1, args.steps + args.warmup))
+    tflops, ms, info = cpu_reference_rate(cfg, per_step, steps=args.steps, warmup=args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": n_gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": args.scaling if n_gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(cfg, n_gpus, args),
+        "cpu_baseline": info,
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(cfg, n_gpus, args):
+    return {
+        "workload": f"{cfg.name}: N={cfg.N} H={cfg.H} V={cfg.V} {str(cfg.dtype).split('.')[-1]} "
+                    f"N_chunk_size={cfg.N_chunk_size} logit_scale={cfg.logit_scale} "
+                    f"z_regularization={cfg.z_regularization} monitoring={cfg.monitoring}",
+        "N": cfg.N, "H": cfg.H, "V": cfg.V, "N_chunk_size": cfg.N_chunk_size,
+        "vocab_sharding": f"{n_gpus} x {cfg.V // n_gpus} columns" if n_gpus > 1 else "none",
+        "l2": "inputs larger than L2 (the weight alone is >= 512 MiB per GPU); no explicit flush",
+    }
+
+
+# ---------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.gpus > 1 and world == 1 and args.impl == "ours":
+        # convenience: relaunch under torch.distributed.run, one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 400), str(Path(__file__))]
+        sys.exit(subprocess.call(cmd + sys.argv[1:]))
+
+    from linear_cross_entropy_loss_b200 import synthetic
+
+    n_gpus = max(args.gpus, world)
+    base = synthetic.CONFIGS[args.config]
+    cfg = base
+    if n_gpus > 1 and args.scaling == "weak":
+        cfg = synthetic.scaled(base, V=base.V * n_gpus, name=f"{base.name}_x{n_gpus}vocab")
+
+    if args.impl == "reference":
+        if rank == 0:
+            run_reference_arm(args, cfg, n_gpus)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from linear_cross_entropy_loss_b200 import _native, linear_cross_entropy
+    from linear_cross_entropy_loss_b200.sharded import linear_cross_entropy_sharded
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    sharded = world > 1
+    if sharded:
+        dist.init_process_group("nccl", device_id=dev)
+    v_local = cfg.V // world
+    x, y, W = synthetic.make_inputs(cfg, device=dev,
+                                    vocab_slice=(rank * v_local, (rank + 1) * v_local) if sharded else None)
+    x.requires_grad_(True)
+    W.requires_grad_(True)
+
+    def fwd_bwd(xx, yy):
+        if sharded:
+            loss = linear_cross_entropy_sharded(xx, yy, W, None, cfg.ignore_index, cfg.z_regularization,
+                                                cfg.logit_scale, cfg.N_chunk_size, cfg.monitoring)[0]
+        else:
+            loss = linear_cross_entropy(xx, yy, W, cfg.ignore_index, cfg.z_regularization, cfg.logit_scale,
+                                        cfg.N_chunk_size, cfg.monitoring)[0]
+        loss.backward()
+        xx.grad = None
+        W.grad = None
+        return loss
+
+    def barrier():
+        if sharded:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if not sharded:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    # ---- device-resident throughput -----------------------------------------------------------------
+    for _ in range(max(3, args.warmup)):
+        fwd_bwd(x, y)
+    barrier()
+    torch.cuda.reset_peak_memory_stats()
+    mem_before = torch.cuda.memory_allocated()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    _native.profile_read()
+    _native.profile_enable(True)
+    launches_before = _native.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        loss = fwd_bwd(x, y)
+    e1.record()
+    barrier()
+    launches = _native.launch_count() - launches_before
+    _native.profile_enable(False)
+    kernel_ms, kernel_launches = _native.profile_read()
+    clocks = sampler.stop()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_per_step = ms_total / args.steps
+    peak_extra = torch.cuda.max_memory_allocated() - mem_before
+    value = cfg.flops / (ms_per_step * 1e-3) / 1e12
+    loss_value = loss.item()
+
+    # ---- end to end through the public call, inputs in pinned host memory ------------------------------
+    x_host = x.detach().to("cpu").pin_memory()
+    y_host = y.to("cpu").pin_memory()
+    x_dev = torch.empty_like(x_host, device=dev).requires_grad_(True)
+    y_dev = torch.empty_like(y_host, device=dev)
+
+    def e2e_step():
+        with torch.no_grad():
+            x_dev.copy_(x_host, non_blocking=True)
+            y_dev.copy_(y_host, non_blocking=True)
+        return fwd_bwd(x_dev, y_dev).item()   # device -> host read of the loss
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    e2e_value = cfg.flops / (e2e_ms * 1e-3) / 1e12
+
+    # ---- roofline of the dominant kernel --------------------------------------------------------------
+    peaks, peak_source = load_peaks()
+    peak_tflops = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    per_launch_flops = 2.0 * min(cfg.N, cfg.N_chunk_size) * cfg.H * v_local   # one contraction over one row chunk
+    kernels = {}
+    for k in ("fwd", "dx", "dw"):
+        if kernel_launches[k] > 0:
+            avg_ms = kernel_ms[k] / kernel_launches[k]
+            kernels[k] = {"launches_per_step": kernel_launches[k] / args.steps, "avg_ms": avg_ms,
+                          "tflops": per_launch_flops / (avg_ms * 1e-3) / 1e12,
+                          "share_of_step": kernel_ms[k] / (ms_per_step * args.steps)}
+    dominant = max(kernels, key=lambda k: kernels[k]["avg_ms"] * kernels[k]["launches_per_step"]) if kernels else None
+    roofline = None
+    if dominant is not None:
+        achieved = kernels[dominant]["tflops"]
+        roofline = {"bound": "tensor", "kernel": f"lce_gemm_kernel[{dominant}]", "achieved": achieved,
+                    "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved / peak_tflops,
+                    "peak_source": f"{peak_source} cuBLAS bf16 GEMM, sustained",
+                    "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(dominant),
+                    "flops_per_launch": per_launch_flops, "kernels": kernels,
+                    "whole_step_frac": (value / world) / peak_tflops}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": args.scaling if world > 1 else "weak",
+        "vs_baseline": value / PUBLISHED_BF16_DEFAULT_TFLOPS if (world == 1 and cfg.name == "headline_bf16") else None,
+        "dtype": str(cfg.dtype).split(".")[-1].replace("bfloat16", "bf16").replace("float16", "f16").replace("float32", "tf32"),
+        "data": "synthetic", "config": config_dict(cfg, world, args), "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": x_host.numel() * x_host.element_size() + y_host.numel() * 8,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": launches, "roofline": roofline, "loss": loss_value,
+        "peak_extra_bytes": peak_extra, "peak_budget_bytes": min(cfg.N, cfg.N_chunk_size) * v_local * 4,
+    }
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        _, _, info = cpu_reference_rate(cfg, args.cpu_seconds)
+        line["cpu_baseline"] = info
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if sharded:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

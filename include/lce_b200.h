@@ -124,6 +124,15 @@ int lce_grad_scale_cast(const void* src, int32_t src_dtype, int64_t src_ld, void
  * (LCE_ERR_DEVICE_TIMEOUT if a bounded in-kernel wait ran out). Debugging / tests. */
 int lce_read_status(void* workspace, void* stream);
 
+/* ---- measurement ------------------------------------------------------------------------------
+ * With profiling enabled, a CUDA event pair is recorded on the launching stream around each of the
+ * three tensor-core contractions (0: logits z = x W, 1: dx = dZ W^T, 2: dW = x^T dZ).
+ * lce_profile_read waits for the recorded events, returns per contraction the summed device time in
+ * milliseconds and the number of launches since the previous read, and resets both.
+ * Plays the part of the reference benchmark's do_bench timing (bench_fusions.py:280-281), per kernel. */
+int lce_profile_enable(int32_t enable);
+int lce_profile_read(double* ms3, long long* launches3);
+
 /* ---- diagnostics ------------------------------------------------------------------------------
  * Runs the GEMM engine alone: out[s][M, N] = A * B^T over K-split s (fp32, row stride N).
  * a_mn_major == 0: a is [M, K] (K contiguous, row stride a_ld); != 0: a is [K, M] (row stride a_ld).

@@ -111,6 +111,8 @@ SIGNATURES = {
     "lce_finalize": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _vp, _vp]),
     "lce_grad_scale_cast": (ctypes.c_int, [_vp, _i32, _i64, _vp, _i32, _i64, _i64, _i64, _vp, _vp]),
     "lce_read_status": (ctypes.c_int, [_vp, _vp]),
+    "lce_profile_enable": (ctypes.c_int, [_i32]),
+    "lce_profile_read": (ctypes.c_int, [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]),
     "lce_debug_gemm": (
         ctypes.c_int,
         [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _vp, _vp],
@@ -145,3 +147,16 @@ def check(status: int, where: str) -> None:
 
 def launch_count() -> int:
     return int(load().lce_launch_count())
+
+
+def profile_enable(on: bool) -> None:
+    check(load().lce_profile_enable(1 if on else 0), "lce_profile_enable")
+
+
+def profile_read():
+    """({"fwd": ms, "dx": ms, "dw": ms}, {"fwd": launches, ...}) since the previous read."""
+    ms = (ctypes.c_double * 3)()
+    n = (ctypes.c_longlong * 3)()
+    check(load().lce_profile_read(ms, n), "lce_profile_read")
+    names = ("fwd", "dx", "dw")
+    return {k: ms[i] for i, k in enumerate(names)}, {k: int(n[i]) for i, k in enumerate(names)}

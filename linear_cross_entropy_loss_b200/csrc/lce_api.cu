@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 namespace {
 
@@ -215,6 +216,42 @@ int check_launch() {
   return cudaGetLastError() == cudaSuccess ? LCE_OK : LCE_ERR_CUDA;
 }
 
+// Optional per-launch timing of the three tensor-core contractions (lce_profile_enable): a CUDA event
+// pair is recorded on the launching stream around each GEMM kernel and read back by lce_profile_read.
+enum : int { PROF_FWD = 0, PROF_DX = 1, PROF_DW = 2, PROF_KINDS = 3 };
+struct ProfSpan {
+  cudaEvent_t start, stop;
+  int kind;
+};
+std::mutex g_prof_mutex;
+bool g_prof_enabled = false;
+std::vector<ProfSpan> g_prof_spans;      // recorded since the last read
+std::vector<ProfSpan> g_prof_free;       // event pairs ready for reuse
+
+struct ProfScope {
+  cudaStream_t st;
+  ProfSpan span;
+  bool active = false;
+  ProfScope(int kind, cudaStream_t stream) : st(stream) {
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    if (!g_prof_enabled) return;
+    if (!g_prof_free.empty()) {
+      span = g_prof_free.back();
+      g_prof_free.pop_back();
+    } else if (cudaEventCreate(&span.start) != cudaSuccess || cudaEventCreate(&span.stop) != cudaSuccess) {
+      return;
+    }
+    span.kind = kind;
+    active = cudaEventRecord(span.start, st) == cudaSuccess;
+  }
+  ~ProfScope() {
+    if (!active) return;
+    cudaEventRecord(span.stop, st);
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    g_prof_spans.push_back(span);
+  }
+};
+
 template <int kKind, bool kAMN, bool kBMN, int kEpi, bool kMon>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& gp, int sms, cudaStream_t st) {
   const long long units = (long long)gp.splits * gp.n_tiles * gp.m_tiles;
@@ -338,8 +375,11 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
   gp.scale = p->logit_scale;
   gp.status = &w.scalars->status;
 
-  v = p->monitoring ? launch_gemm_dtype<false, true, EPI_FWD, true>(p->dtype, ta, tb, gp, sms, st)
-                    : launch_gemm_dtype<false, true, EPI_FWD, false>(p->dtype, ta, tb, gp, sms, st);
+  {
+    ProfScope prof(PROF_FWD, st);
+    v = p->monitoring ? launch_gemm_dtype<false, true, EPI_FWD, true>(p->dtype, ta, tb, gp, sms, st)
+                      : launch_gemm_dtype<false, true, EPI_FWD, false>(p->dtype, ta, tb, gp, sms, st);
+  }
   if (v != LCE_OK) return v;
 
   const int blocks = (int)((rows + 31) / 32);
@@ -436,7 +476,11 @@ int lce_backward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const 
     gp.out_scale = p->logit_scale;
     gp.out_div = &w.scalars->n_valid;
     gp.status = &w.scalars->status;
-    if ((v = launch_gemm_dtype<false, false, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st)) != LCE_OK) return v;
+    {
+      ProfScope prof(PROF_DX, st);
+      v = launch_gemm_dtype<false, false, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st);
+    }
+    if (v != LCE_OK) return v;
 
     const long long quads = rows * (p->hidden / 4);
     const int grid = grid_for(quads, 256, sms, 8);
@@ -479,7 +523,11 @@ int lce_backward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const 
     gp.out_scale = p->logit_scale;
     gp.out_div = &w.scalars->n_valid;
     gp.status = &w.scalars->status;
-    if ((v = launch_gemm_dtype<true, true, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st)) != LCE_OK) return v;
+    {
+      ProfScope prof(PROF_DW, st);
+      v = launch_gemm_dtype<true, true, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st);
+    }
+    if (v != LCE_OK) return v;
   }
   return LCE_OK;
 }
@@ -550,6 +598,34 @@ int lce_read_status(void* workspace, void* stream) {
     return LCE_ERR_CUDA;
   if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return LCE_ERR_CUDA;
   return host.status == 0 ? LCE_OK : LCE_ERR_DEVICE_TIMEOUT;
+}
+
+int lce_profile_enable(int32_t enable) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  g_prof_enabled = enable != 0;
+  return LCE_OK;
+}
+
+int lce_profile_read(double* ms3, long long* launches3) {
+  if (!ms3 || !launches3) return LCE_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  for (int k = 0; k < PROF_KINDS; ++k) {
+    ms3[k] = 0.0;
+    launches3[k] = 0;
+  }
+  int rc = LCE_OK;
+  for (const ProfSpan& sp : g_prof_spans) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(sp.stop) != cudaSuccess || cudaEventElapsedTime(&ms, sp.start, sp.stop) != cudaSuccess) {
+      rc = LCE_ERR_CUDA;
+    } else {
+      ms3[sp.kind] += ms;
+      launches3[sp.kind] += 1;
+    }
+    g_prof_free.push_back(sp);
+  }
+  g_prof_spans.clear();
+  return rc;
 }
 
 int lce_debug_gemm(int32_t dtype, int32_t a_mn_major, int32_t b_mn_major, const void* a, int64_t a_ld, const void* b,

@@ -15,6 +15,7 @@ device memory, streams and the chunk loop. There is no CPU or eager fallback.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import math
 from dataclasses import dataclass
@@ -41,6 +42,7 @@ class NativeBackend:
     """Calls into liblce_b200.so on the current CUDA stream of the tensors' device."""
 
     name = "liblce_b200"
+    requires_cuda = True
 
     def __init__(self):
         self.lib = _native.load()
@@ -152,6 +154,8 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     want_grad. Follows the chunk loop of the reference (ops.py:721-791).
     """
     backend = get_backend()
+    if getattr(backend, "requires_cuda", True) and not (x.is_cuda and y.is_cuda and At.is_cuda):
+        raise RuntimeError("linear_cross_entropy_loss_b200 runs on CUDA tensors only; there is no CPU fallback")
     N, H = x.shape
     H_A, V = At.shape
     assert H_A == H, "x and the weight disagree on the hidden size"
@@ -198,6 +202,11 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     return out5, dx, dA, workspace
 
 
+def _device_guard(t: torch.Tensor):
+    """Makes the tensor's GPU current (needed for devices other than 0, as in reference ops.py:680)."""
+    return torch.cuda.device(t.device) if t.is_cuda else contextlib.nullcontext()
+
+
 def _prepare(x_in, y, At):
     x = x_in.reshape(-1, x_in.shape[-1])
     if x.stride(-1) != 1 or (x.stride(0) * x.element_size()) % 16 != 0:
@@ -233,7 +242,7 @@ class LinearXentImplementation(torch.autograd.Function):
                 N_chunk_size: int = 4096, monitoring: bool = True):
         # Under CUDA autocast the decorator casts floating inputs to fp16 and disables autocast
         # inside, exactly as the reference does (ops.py:665-667).
-        with torch.cuda.device(x_in.device):
+        with _device_guard(x_in):
             x, y_flat, A = _prepare(x_in, y, At)
             want_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[2])
             with torch.no_grad():
@@ -251,7 +260,7 @@ class LinearXentImplementation(torch.autograd.Function):
     def backward(ctx, grad_output, void0, void1, void2, void3):
         if ctx.lce_grads is None:
             raise RuntimeError("backward called twice, or forward ran without any input requiring grad")
-        with torch.cuda.device(grad_output.device), torch.no_grad():
+        with _device_guard(grad_output), torch.no_grad():
             gx, gA = _scaled_grads(ctx, grad_output)
         return gx, None, gA, None, None, None, None, None
 

@@ -1,0 +1,156 @@
+"""Vocabulary-sharded execution of the fused loss over the GPUs of one node.
+
+Rank g of a process group holds the column slab ``W[:, g*V/G:(g+1)*V/G]`` of the (H, V) weight; ``x``
+and ``y`` are replicated. Per row chunk:
+
+1. every rank runs the forward GEMM on its slab and produces five per-row partials
+   (max, sum exp, target logit, sum exp*z, sum z^2);
+2. ONE small all-gather (``5 * chunk_rows`` floats per rank) makes all partials visible everywhere and a
+   local kernel merges them in rank order into the global log-sum-exp -- bitwise identical on every
+   rank, which a max/sum all-reduce pair would not guarantee;
+3. every rank forms dZ for its slab, its own dW slab (no communication) and a partial dx, which is
+   summed over the ranks with an all-reduce that runs asynchronously while the next chunk computes.
+
+The reference has no multi-GPU path; the collectives here are NCCL through ``torch.distributed`` (gloo on
+CPU in the unit tests). Loss and metrics come out identical on all ranks.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+from ._native import ROW_PARTS
+
+
+class _Collectives:
+    """The two per-chunk exchanges of one pass, with their scratch buffer and pending work handles."""
+
+    def __init__(self, group, world: int):
+        self.group = group
+        self.world = world
+        self.gathered: Optional[torch.Tensor] = None
+        self.pending = []
+
+    def gather_row_parts(self, local: torch.Tensor) -> torch.Tensor:
+        if self.gathered is None:
+            self.gathered = torch.empty(self.world * local.numel(), dtype=local.dtype, device=local.device)
+        try:
+            dist.all_gather_into_tensor(self.gathered, local, group=self.group)
+        except (RuntimeError, NotImplementedError):  # backend without a flat all-gather
+            dist.all_gather(list(self.gathered.chunk(self.world)), local, group=self.group)
+        return self.gathered
+
+    def reduce_dx(self, dx_rows: torch.Tensor) -> None:
+        # asynchronous: the next chunk's GEMMs overlap the transfer; joined in wait_all()
+        self.pending.append(dist.all_reduce(dx_rows, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    def wait_all(self) -> None:
+        for work in self.pending:
+            work.wait()
+        self.pending.clear()
+
+
+class VocabShardedLinearXent(torch.autograd.Function):
+    """Sharded counterpart of ``ops.LinearXentImplementation``: same outputs, W given as this rank's slab."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float16)
+    def forward(ctx, x_in, y, At_shard, group=None, ignore_index=-100, z_regularization: float = 0.0,
+                logit_scale: float = 1.0, N_chunk_size: int = 4096, monitoring: bool = False):
+        world = dist.get_world_size(group)
+        rank = dist.get_rank(group)
+        with ops._device_guard(x_in):
+            x, y_flat, A = ops._prepare(x_in, y, At_shard)
+            v_local = A.shape[1]
+            coll = _Collectives(group, world)
+            spec = ops.ShardSpec(rank=rank, world=world, vocab_offset=rank * v_local,
+                                 gather_row_parts=coll.gather_row_parts, reduce_dx=coll.reduce_dx)
+            want_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[2])
+            with torch.no_grad():
+                out5, dx, dA, _ = ops.run_pass(x, y_flat, A, ignore_index, z_regularization, logit_scale,
+                                               N_chunk_size, monitoring, want_grad, shard=spec)
+                coll.wait_all()
+            ctx.lce_grads = (dx, dA) if want_grad else None
+            ctx.lce_dtypes = (x_in.dtype, At_shard.dtype)
+            ctx.lce_x_shape = x_in.shape
+            loss, z_value, logit_max, logit_ent, logit_norm = out5.unbind(0)
+            ctx.mark_non_differentiable(z_value, logit_max, logit_ent, logit_norm)
+            return loss, z_value, logit_max, logit_ent, logit_norm
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, grad_output, void0, void1, void2, void3):
+        if ctx.lce_grads is None:
+            raise RuntimeError("backward called twice, or forward ran without any input requiring grad")
+        with ops._device_guard(grad_output), torch.no_grad():
+            gx, gA = ops._scaled_grads(ctx, grad_output)
+        return gx, None, gA, None, None, None, None, None, None
+
+
+def linear_cross_entropy_sharded(x, y, At_shard, group=None, ignore_index=-100, z_regularization: float = 0.0,
+                                 logit_scale: float = 1.0, N_chunk_size: int = 4096, monitoring: bool = False):
+    """``linear_cross_entropy`` with W sharded by columns over ``group``. x and y must be equal on all ranks.
+
+    Returns the same 5-tuple on every rank. ``x.grad`` is the full gradient (summed over the shards),
+    ``At_shard.grad`` is the gradient of this rank's slab.
+    """
+    return VocabShardedLinearXent.apply(x, y, At_shard, group, ignore_index, z_regularization, logit_scale,
+                                        N_chunk_size, monitoring)
+
+
+class VocabShardedLinearCrossEntropyLoss(torch.nn.Module):
+    """``LinearCrossEntropyLoss`` whose weight is this rank's ``(in_features, out_features / world)`` slab.
+
+    ``full_weight_init`` (default) draws the whole ``(in_features, out_features)`` matrix from one seeded
+    generator on every rank and keeps the local columns, so the sharded module starts from the same
+    weights as an unsharded one built with the same ``init_seed``.
+    """
+
+    def __init__(self, in_features: int, out_features: int, group=None, device=None, dtype=None,
+                 ignore_index: int = -100, logit_scale: float = 1.0, z_regularization: float = 0.0,
+                 N_chunk_size: int = 4096, init_seed: int = 0):
+        super().__init__()
+        world = dist.get_world_size(group)
+        rank = dist.get_rank(group)
+        assert in_features % 256 == 0
+        assert out_features % (256 * world) == 0, "every rank's slab must be a multiple of 256 columns"
+        assert N_chunk_size % 128 == 0
+        assert logit_scale > 0 and z_regularization >= 0
+        self.group = group
+        self.in_features, self.out_features = in_features, out_features
+        self.local_features = out_features // world
+        self.vocab_offset = rank * self.local_features
+        self.ignore_index, self.logit_scale = ignore_index, logit_scale
+        self.z_regularization, self.N_chunk_size = z_regularization, N_chunk_size
+        self.monitoring = False
+        self.latest_metrics = {}
+        self.weight = torch.nn.Parameter(torch.empty((in_features, self.local_features), device=device, dtype=dtype))
+        self.reset_parameters(init_seed)
+
+    def reset_parameters(self, seed: int = 0) -> None:
+        std = math.sqrt(1 / self.in_features)
+        g = torch.Generator().manual_seed(seed)
+        with torch.no_grad():
+            for h0 in range(0, self.in_features, 64):
+                h1 = min(self.in_features, h0 + 64)
+                blk = torch.empty((h1 - h0, self.out_features))
+                torch.nn.init.trunc_normal_(blk, mean=0.0, std=std, a=-3 * std, b=3 * std, generator=g)
+                self.weight[h0:h1] = blk[:, self.vocab_offset:self.vocab_offset + self.local_features].to(
+                    device=self.weight.device, dtype=self.weight.dtype)
+
+    def forward(self, x, y):
+        loss, z_reg, logit_max, logit_ent, logit_norm = linear_cross_entropy_sharded(
+            x, y, self.weight, self.group, self.ignore_index, self.z_regularization, self.logit_scale,
+            self.N_chunk_size, self.monitoring)
+        if self.monitoring:
+            self.latest_metrics = {"logit_norm": logit_norm, "logit_max": logit_max, "logit_entropy": logit_ent,
+                                   "z_value": z_reg}
+        return loss
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, "
+                f"local_features={self.local_features}, bias=False")

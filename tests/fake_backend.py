@@ -1,0 +1,87 @@
+"""A stand-in for liblce_b200 that computes each per-chunk call with the float64 oracle on the CPU.
+
+Only used by the CPU tests of the HOST logic (chunk loop, autograd plumbing, vocabulary sharding over
+gloo); it mirrors the methods of ``ops.NativeBackend`` one for one.
+"""
+import numpy as np
+import torch
+
+from oracle import oracle
+
+
+class FakeBackend:
+    name = "oracle-fake"
+    requires_cuda = False
+
+    def __init__(self):
+        self.state = {}
+        self.calls = []
+
+    def workspace_bytes(self, prob):
+        return 256
+
+    def begin(self, prob, y, workspace):
+        self.calls.append("begin")
+        self.state[workspace.data_ptr()] = dict(
+            n_valid=float((y != prob.ignore_index).sum()), nll=0.0, lse2=0.0, ent=0.0, norm=0.0, zmax=-np.inf,
+        )
+
+    def forward_chunk(self, prob, x, At, y, row0, rows, workspace, row_parts):
+        self.calls.append("forward_chunk")
+        st = self.state[workspace.data_ptr()]
+        z = oracle.logits64(x[row0:row0 + rows], At, prob.logit_scale)
+        yy = y[row0:row0 + rows].numpy()
+        parts = oracle.row_partials(z, yy, prob.vocab_offset, prob.ignore_index)
+        rp = row_parts.view(5, prob.chunk_rows)
+        rp[:, :rows] = torch.from_numpy(parts).float()
+        st["z"] = z
+
+    def combine_chunk(self, prob, row_parts_all, y, row0, rows, workspace):
+        self.calls.append("combine_chunk")
+        st = self.state[workspace.data_ptr()]
+        parts = row_parts_all.view(prob.world, 5, prob.chunk_rows)[:, :, :rows].double().numpy()
+        lse, t, ent, q, m = oracle.combine_partials(parts)
+        v = (y[row0:row0 + rows] != prob.ignore_index).numpy()
+        st["nll"] += float(((lse - t) * v).sum())
+        st["lse2"] += float((lse * lse * v).sum())
+        st["ent"] += float((ent * v).sum())
+        st["norm"] += float(np.sqrt(q).sum())
+        st["zmax"] = max(st["zmax"], float(m.max()))
+        st["lse"] = lse
+
+    def backward_chunk(self, prob, x, At, y, row0, rows, workspace, dx, dA, first_chunk):
+        self.calls.append("backward_chunk")
+        st = self.state[workspace.data_ptr()]
+        z, lse = st["z"], st["lse"]
+        yy = y[row0:row0 + rows].numpy()
+        v = yy != prob.ignore_index
+        p = np.exp(z - lse[:, None]) * (1.0 + 2.0 * prob.z_regularization * lse)[:, None]
+        yl = yy - prob.vocab_offset
+        own = v & (yl >= 0) & (yl < z.shape[1])
+        p[np.nonzero(own)[0], yl[own]] -= 1.0
+        p *= v[:, None]
+        coef = prob.logit_scale / st["n_valid"]
+        dx[row0:row0 + rows] = torch.from_numpy(p @ At.double().numpy().T * coef).to(dx.dtype)
+        g = torch.from_numpy(x[row0:row0 + rows].double().numpy().T @ p * coef).float()
+        if first_chunk:
+            dA.copy_(g)
+        else:
+            dA.add_(g)
+
+    def finalize(self, prob, workspace, out5):
+        self.calls.append("finalize")
+        st = self.state.pop(workspace.data_ptr())
+        R = st["n_valid"]
+        with np.errstate(invalid="ignore", divide="ignore"):
+            vals = [
+                np.float64(st["nll"] + prob.z_regularization * st["lse2"]) / R, np.float64(st["lse2"]) / R,
+                st["zmax"], np.float64(st["ent"]) / R, st["norm"] / prob.n_rows_total,
+            ]
+        out5.copy_(torch.tensor(vals, dtype=torch.float32))
+
+    def grad_scale_cast(self, src, dst, factor):
+        self.calls.append("grad_scale_cast")
+        dst.copy_((src.double() * factor.double()).to(dst.dtype))
+
+    def read_status(self, workspace):
+        return 0

@@ -1,0 +1,45 @@
+"""Child process of tests/test_gpu_sharded.py: one rank of a vocabulary-sharded pass over NCCL."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+from gpu_util import cosine, random_problem  # noqa: E402
+from linear_cross_entropy_loss_b200.sharded import linear_cross_entropy_sharded  # noqa: E402
+from oracle import oracle  # noqa: E402
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl")
+    N, H, V = 1024, 512, 8192
+    x, y, W = random_problem(N, H, V, torch.bfloat16, seed=0)
+    vl = V // world
+    xd = x.cuda().requires_grad_(True)
+    Ws = W[:, rank * vl:(rank + 1) * vl].contiguous().cuda().requires_grad_(True)
+    out = linear_cross_entropy_sharded(xd, y.cuda(), Ws, None, -1, 1e-4, 0.5, 256, True)
+    out[0].backward()
+    torch.cuda.synchronize()
+    ref = oracle.forward_backward(x, y, W, -1, 1e-4, 0.5)
+    ok = abs(out[0].item() - ref.loss) < 2e-5 * ref.loss
+    ok &= cosine(xd.grad.double().cpu().numpy(), ref.dx) > 0.99999
+    ok &= cosine(Ws.grad.double().cpu().numpy(), ref.dW[:, rank * vl:(rank + 1) * vl]) > 0.99999
+    flag = torch.tensor([1.0 if ok else 0.0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0 and flag.item() == 1.0:
+        print("SHARDED_OK")
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 1.0 else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,110 @@
+"""The C-ABI shared library without a GPU: it builds, loads, exports every symbol the header declares,
+and rejects bad arguments with status codes before touching a device."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from linear_cross_entropy_loss_b200 import _native
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = (ROOT / "include" / "lce_b200.h").read_text()
+
+
+@pytest.fixture(scope="module")
+def lib():
+    return _native.load()
+
+
+def declared_functions():
+    return sorted(set(re.findall(r"^(?:int|long long|const char\*)\s+(lce_\w+)\s*\(", HEADER, flags=re.M)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_functions()
+    for required in ["lce_begin", "lce_forward_chunk", "lce_combine_chunk", "lce_backward_chunk", "lce_finalize",
+                     "lce_grad_scale_cast", "lce_workspace_bytes", "lce_status_string", "lce_version"]:
+        assert required in names
+
+
+def test_library_exports_every_declared_symbol(lib):
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} is declared in lce_b200.h but not exported"
+    assert set(_native.SIGNATURES) == set(declared_functions())
+
+
+def test_every_entry_point_cites_the_reference_or_says_it_has_no_counterpart():
+    assert HEADER.count("ops.py:") >= 8
+    assert "No counterpart in the reference" in HEADER
+
+
+def test_version_and_status_strings(lib):
+    assert lib.lce_version() >= 100
+    assert _native.status_string(0) == "ok"
+    seen = {_native.status_string(code) for code in range(-8, 1)}
+    assert len(seen) == 9 and "unknown status" not in seen
+    assert _native.status_string(-99) == "unknown status"
+
+
+def problem(**kw):
+    base = dict(n_rows_total=1024, chunk_rows=256, hidden=256, vocab_local=4096, vocab_offset=0, ignore_index=-100,
+                world=1, dtype=_native.DTYPE_BF16, monitoring=0, want_grad=1, logit_scale=1.0, z_regularization=0.0)
+    base.update(kw)
+    return _native.Problem(**base)
+
+
+def workspace_bytes(lib, p):
+    out = ctypes.c_size_t(0)
+    return lib.lce_workspace_bytes(ctypes.byref(p), ctypes.byref(out)), out.value
+
+
+def test_workspace_size_accounts_for_slab_statistics_and_partials(lib):
+    rc, nbytes = workspace_bytes(lib, problem())
+    assert rc == 0
+    slab = 256 * 4096 * 2
+    stats = 2 * (4096 // 256) * 256 * 4
+    assert nbytes >= slab + stats + 256 * 256 * 4
+    assert nbytes < 2 * (slab + stats) + 16 * 256 * 256 * 4
+    rc, fwd_only = workspace_bytes(lib, problem(want_grad=0))
+    assert rc == 0 and fwd_only < slab
+    rc, mon = workspace_bytes(lib, problem(monitoring=1))
+    assert rc == 0 and mon == nbytes + stats
+    # headline shape: slab + split-K partials stay below N_chunk x V x 4 bytes
+    rc, big = workspace_bytes(lib, problem(n_rows_total=16384, chunk_rows=4096, hidden=2048, vocab_local=131072))
+    assert rc == 0 and big <= 4096 * 131072 * 4
+
+
+@pytest.mark.parametrize("kw,code", [
+    (dict(dtype=7), -1), (dict(hidden=0), -1), (dict(logit_scale=0.0), -1), (dict(z_regularization=-1.0), -1),
+    (dict(world=0), -1), (dict(chunk_rows=2048), -1),
+    (dict(hidden=384), -2), (dict(vocab_local=4000), -2), (dict(chunk_rows=192), -2), (dict(n_rows_total=1000), -2),
+    (dict(vocab_local=1 << 31), -8),
+])
+def test_invalid_problems_are_rejected_without_a_device(lib, kw, code):
+    rc, _ = workspace_bytes(lib, problem(**kw))
+    assert rc == code
+    # the same validation guards the launching entry points (checked before any CUDA call)
+    assert lib.lce_begin(ctypes.byref(problem(**kw)), 16, 16, None) == code
+
+
+def test_null_pointers_are_rejected(lib):
+    p = problem()
+    assert lib.lce_begin(ctypes.byref(p), None, None, None) == -1
+    assert lib.lce_forward_chunk(ctypes.byref(p), None, 256, None, 4096, None, 0, 256, None, None, None) == -1
+    assert lib.lce_finalize(ctypes.byref(p), None, None, None) == -1
+    assert lib.lce_grad_scale_cast(None, 0, 1, None, 0, 1, 1, 1, None, None) == -1
+    assert lib.lce_read_status(None, None) == -1
+    assert lib.lce_workspace_bytes(None, None) == -1
+
+
+def test_chunk_bounds_are_checked(lib):
+    p = problem()
+    args = (16, 256, 16, 4096, 16)
+    assert lib.lce_forward_chunk(ctypes.byref(p), *args, 0, 512, 16, 16, None) == -1    # more rows than a chunk
+    assert lib.lce_forward_chunk(ctypes.byref(p), *args, 1024, 256, 16, 16, None) == -1  # past the end
+    assert lib.lce_forward_chunk(ctypes.byref(p), *args, 64, 128, 16, 16, None) == -2    # unaligned start
+
+
+def test_launch_counter_starts_at_zero_without_a_gpu(lib):
+    assert lib.lce_launch_count() >= 0

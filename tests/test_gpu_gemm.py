@@ -1,0 +1,63 @@
+"""The tcgen05 GEMM engine alone (lce_debug_gemm): every operand layout of the three contractions, for each
+input type, against a float64 product."""
+import pytest
+import torch
+
+from linear_cross_entropy_loss_b200 import _native
+
+pytestmark = pytest.mark.gpu
+
+CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+
+def run(dtype, a_mn, b_mn, M, N, K, splits=1, seed=0):
+    lib = _native.load()
+    g = torch.Generator().manual_seed(seed)
+    A = torch.randn(M, K, generator=g).to(dtype)
+    B = torch.randn(N, K, generator=g).to(dtype)
+    ref = A.double() @ B.double().T
+    a = (A.T.contiguous() if a_mn else A).cuda()
+    b = (B.T.contiguous() if b_mn else B).cuda()
+    out = torch.full((splits, M, N), float("nan"), dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = lib.lce_debug_gemm(CODE[dtype], a_mn, b_mn, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
+                            out.data_ptr(), M, N, K, splits, status.data_ptr(),
+                            torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _native.status_string(rc)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    got = out.double().sum(0).cpu()
+    return (got - ref).abs().max().item() / ref.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 1), (0, 0), (1, 1), (1, 0)])
+def test_all_operand_layouts(dtype, a_mn, b_mn):
+    # (0,1) logits z = x W, (0,0) dx = dZ W^T, (1,1) dW = x^T dZ
+    tol = 2e-3 if dtype == torch.float32 else 1e-5   # TF32 keeps 10 mantissa bits of each input
+    assert run(dtype, a_mn, b_mn, 256, 512, 512) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_split_k_partials_sum_to_the_product(dtype):
+    tol = 2e-3 if dtype == torch.float32 else 1e-5
+    assert run(dtype, 0, 0, 256, 256, 4096, splits=4) < tol
+
+
+def test_more_tiles_than_sms_and_long_k():
+    assert run(torch.bfloat16, 0, 1, 128 * 23, 256 * 9, 256) < 1e-5     # 207 tiles: several per CTA
+    assert run(torch.float16, 1, 1, 128, 256, 64 * 150) < 1e-4           # 150 K-blocks through a 4-deep ring
+    #                                                                      (fp32 accumulation over K = 9600)
+
+
+def test_shape_errors_are_status_codes():
+    lib = _native.load()
+    t = torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda")
+    o = torch.zeros(256, 256, dtype=torch.float32, device="cuda")
+    s = torch.zeros(1, dtype=torch.int32, device="cuda")
+    call = lambda m, n, k, sp=1: lib.lce_debug_gemm(1, 0, 0, t.data_ptr(), 256, t.data_ptr(), 256, o.data_ptr(), m, n,
+                                                    k, sp, s.data_ptr(), None)
+    assert call(100, 256, 256) == -2
+    assert call(128, 100, 256) == -2
+    assert call(128, 256, 100) == -2
+    assert call(128, 256, 256, 3) == -2

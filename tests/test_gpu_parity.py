@@ -1,0 +1,182 @@
+"""Parity of the CUDA path (called through the C ABI via the Python surface) against the float64 oracle and the
+golden vectors of the reference's torch statement, at sizes the oracle handles in seconds."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN_CASES, golden_case
+from gpu_util import TOL, check_against_oracle, cosine, random_problem, rel_err, run_gpu
+from linear_cross_entropy_loss_b200 import LinearCrossEntropyLoss, linear_cross_entropy, synthetic
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_golden_vectors_of_the_reference(golden, name, dtype):
+    c = golden_case(golden, name)
+    x = torch.tensor(c["x"]).to(dtype)      # multiples of 1/64 and 1/512: exact in every dtype
+    W = torch.tensor(c["W"]).to(dtype)
+    y = torch.tensor(c["y"])
+    got, dx, dW = run_gpu(x, y, W, c["ignore_index"], c["z_regularization"], c["logit_scale"], chunk=128)
+    tol = TOL[dtype]
+    want = c["scalars"]
+    assert abs(got[0] - want[0]) <= tol["loss"] * abs(want[0])
+    assert abs(got[1] - want[1]) <= 2 * tol["loss"] * abs(want[1])
+    assert abs(got[2] - want[2]) <= 2e-3 * abs(want[2])
+    assert abs(got[3] - want[3]) <= 1e-3 * abs(want[3])
+    assert abs(got[4] - want[4]) <= 1e-3 * abs(want[4])
+    dxn, dWn = dx.double().cpu().numpy(), dW.double().cpu().numpy()
+    assert cosine(dxn, c["dx"]) >= tol["cos"]
+    assert cosine(dWn[::16], c["dW_rows"]) >= tol["cos"]
+    mass = np.abs(dWn).sum(axis=0).max()
+    assert np.abs(dWn.sum(axis=0) - c["dW_colsum"]).max() <= 4e-3 * mass
+
+
+def test_config_c1_small_fp32_case():
+    cfg = synthetic.CONFIGS["c1_small_fp32"]
+    x, y, W = synthetic.make_inputs(cfg, device="cpu")
+    check_against_oracle(x, y, W, cfg.dtype, cfg.ignore_index, cfg.z_regularization, cfg.logit_scale, cfg.N_chunk_size)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_reduced_default_configs_with_all_options(dtype):
+    # C2 / C3 options at a size the oracle finishes in seconds
+    x, y, W = random_problem(2048, 512, 8192, dtype, seed=3, ignore=-1, frac=0.02)
+    check_against_oracle(x, y, W, dtype, ignore=-1, zreg=1e-4, scale=0.5, chunk=512)
+    check_against_oracle(x, y, W, dtype, ignore=-1, zreg=0.0, scale=1.0, chunk=1024, monitoring=False)
+
+
+@pytest.mark.parametrize("H,N,V", [(512, 1024, 4096), (1024, 512, 4096), (256, 2048, 16384), (2048, 256, 2048)])
+def test_accuracy_sweep_bf16(H, N, V):
+    x, y, W = random_problem(N, H, V, torch.bfloat16, seed=H + N)
+    check_against_oracle(x, y, W, torch.bfloat16, ignore=-1, zreg=1e-4, scale=0.5, chunk=512)
+
+
+def test_low_loss_recipe_of_the_reference_benchmarks():
+    # the reference's accuracy benchmark plants the label direction into x (bench_fusions.py:480-486)
+    g = torch.Generator().manual_seed(0)
+    N, H, V = 1024, 256, 4096
+    A = torch.randn(V, H, generator=g)
+    y = torch.randint(0, V, (N,), generator=g)
+    x = (0.1 * A[y] + torch.randn(N, H, generator=g)).half()
+    W = A.t().contiguous().half()
+    got, dxn, dWn, ref = check_against_oracle(x, y, W, torch.float16, chunk=256)
+    # in the reference's own units (torch.dist): the published fp16 figures are 7e-5 (loss) and 1.4e-4 (grads)
+    assert abs(got[0] - ref.loss) < 1e-4
+    assert 0.5 * (np.linalg.norm(dxn - ref.dx) + np.linalg.norm(dWn - ref.dW)) < 5e-4
+
+
+@pytest.mark.parametrize("chunk,N", [(128, 384), (256, 640), (512, 512), (4096, 256)])
+def test_ragged_last_chunk_and_single_chunk(chunk, N):
+    x, y, W = random_problem(N, 256, 1024, torch.bfloat16, seed=N)
+    check_against_oracle(x, y, W, torch.bfloat16, ignore=-1, chunk=chunk)
+
+
+def test_labels_on_tile_boundaries_and_repeated_labels():
+    x, y, W = random_problem(256, 256, 1024, torch.float16, seed=5, frac=0.0)
+    y[:8] = torch.tensor([0, 255, 256, 511, 512, 767, 768, 1023])
+    y[8:64] = 300
+    check_against_oracle(x, y, W, torch.float16)
+
+
+def test_ignore_index_that_is_a_class_id():
+    x, y, W = random_problem(256, 256, 512, torch.bfloat16, seed=6, frac=0.0)
+    y[:100] = 5
+    got, dxn, dWn, ref = check_against_oracle(x, y, W, torch.bfloat16, ignore=5)
+    assert np.all(dxn[:100] == 0)
+
+
+def test_all_rows_ignored_gives_nan_loss_like_the_reference():
+    x, y, W = random_problem(128, 256, 512, torch.bfloat16, seed=7, frac=0.0)
+    y[:] = -100
+    got, dx, dW = run_gpu(x, y, W)
+    assert np.isnan(got[0])
+
+
+def test_one_valid_row():
+    x, y, W = random_problem(128, 256, 512, torch.float16, seed=8, frac=0.0)
+    y[:] = -100
+    y[77] = 3
+    got, dxn, dWn, ref = check_against_oracle(x, y, W, torch.float16)
+    assert np.count_nonzero(np.abs(dxn).sum(axis=1)) == 1
+
+
+def test_peaked_softmax_large_logit_scale():
+    x, y, W = random_problem(256, 256, 1024, torch.bfloat16, seed=9)
+    check_against_oracle(x, y, W, torch.bfloat16, ignore=-1, scale=16.0, zreg=1e-3)
+
+
+def test_strided_rows_of_x_and_w_are_read_in_place():
+    x, y, W = random_problem(256, 512, 1024, torch.float16, seed=10)
+    xd = x.cuda()[:, :256]            # row stride 512, 256 columns used
+    Wd = W.cuda()[:256, :512]         # row stride 1024
+    xd.requires_grad_(True)
+    Wd.requires_grad_(True)
+    out = linear_cross_entropy(xd, (y % 512).cuda(), Wd, -1)
+    out[0].backward()
+    ref = oracle.forward_backward(x[:, :256], y % 512, W[:256, :512], -1)
+    assert abs(out[0].item() - ref.loss) < 2e-5 * ref.loss
+    assert cosine(xd.grad.double().cpu().numpy(), ref.dx) > 0.999999
+
+
+def test_grad_output_factor_and_dtypes():
+    x, y, W = random_problem(256, 256, 512, torch.bfloat16, seed=11)
+    _, dx1, dW1 = run_gpu(x, y, W, -1)
+    _, dx3, dW3 = run_gpu(x, y, W, -1, grad_scale=3.0)
+    assert dx1.dtype == torch.bfloat16 and dW1.dtype == torch.bfloat16
+    assert rel_err(dx3.double().cpu().numpy(), 3 * dx1.double().cpu().numpy()) < 4e-3
+    assert rel_err(dW3.double().cpu().numpy(), 3 * dW1.double().cpu().numpy()) < 4e-3
+
+
+def test_forward_only_skips_the_gradient_kernels():
+    from linear_cross_entropy_loss_b200 import _native
+    x, y, W = random_problem(256, 256, 512, torch.bfloat16, seed=12)
+    xd, yd, Wd = x.cuda(), y.cuda(), W.cuda()
+    before = _native.launch_count()
+    out = linear_cross_entropy(xd, yd, Wd, -1)
+    fwd_only = _native.launch_count() - before
+    torch.cuda.synchronize()
+    ref = oracle.forward_backward(x, y, W, -1, want_grad=False)
+    assert abs(out[0].item() - ref.loss) < 2e-5 * ref.loss
+    before = _native.launch_count()
+    out = linear_cross_entropy(xd.requires_grad_(True), yd, Wd, -1)
+    assert _native.launch_count() - before > fwd_only
+
+
+def test_module_forward_backward_and_metrics():
+    torch.manual_seed(0)
+    m = LinearCrossEntropyLoss(512, 4096, ignore_index=-1, logit_scale=0.5, z_regularization=1e-4,
+                               N_chunk_size=512).cuda().to(torch.bfloat16)
+    m.monitoring = True
+    x, y, _ = random_problem(1024, 512, 4096, torch.bfloat16, seed=13)
+    xd = x.cuda().view(2, 512, 512).requires_grad_(True)
+    loss = m(xd, y.cuda().view(2, 512))
+    loss.backward()
+    ref = oracle.forward_backward(x, y, m.weight, -1, 1e-4, 0.5)
+    assert abs(loss.item() - ref.loss) < 2e-5 * ref.loss
+    assert set(m.latest_metrics) == {"logit_norm", "logit_max", "logit_entropy", "z_value"}
+    assert abs(m.latest_metrics["logit_entropy"].item() - ref.logit_entropy) < 1e-3 * ref.logit_entropy
+    assert xd.grad.shape == (2, 512, 512)
+    assert cosine(m.weight.grad.double().cpu().numpy(), ref.dW) > 0.99999
+
+
+def test_autocast_casts_inputs_to_fp16_like_the_reference():
+    x, y, W = random_problem(256, 256, 512, torch.float32, seed=14)
+    xd = x.cuda().requires_grad_(True)
+    Wd = W.cuda().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss = linear_cross_entropy(xd, y.cuda(), Wd, -1)[0]
+    loss.backward()
+    assert xd.grad.dtype == torch.float32 and Wd.grad.dtype == torch.float32
+    ref = oracle.forward_backward(x.half(), y, W.half(), -1)
+    assert abs(loss.item() - ref.loss) < 2e-5 * ref.loss
+    assert cosine(xd.grad.double().cpu().numpy(), ref.dx) > 0.999999
+
+
+def test_device_status_is_clean_after_a_pass():
+    from linear_cross_entropy_loss_b200 import ops
+    x, y, W = random_problem(256, 256, 512, torch.bfloat16, seed=15)
+    out5, dx, dA, ws = ops.run_pass(x.cuda(), y.cuda(), W.cuda(), -1, 0.0, 1.0, 128, False, True)
+    assert ops.get_backend().read_status(ws) == 0

@@ -1,0 +1,144 @@
+"""Host-side logic on the CPU: the chunk loop, the autograd plumbing and the module surface, driven through a
+stand-in backend that answers each per-chunk call with the float64 oracle (tests/fake_backend.py).
+The product path itself has no CPU fallback -- that is tested here too."""
+import numpy as np
+import pytest
+import torch
+
+from fake_backend import FakeBackend
+from linear_cross_entropy_loss_b200 import LinearCrossEntropyLoss, linear_cross_entropy, ops
+from oracle import oracle
+
+
+@pytest.fixture
+def fake():
+    backend = FakeBackend()
+    ops.set_backend(backend)
+    yield backend
+    ops.set_backend(None)
+
+
+def make(N=512, H=256, V=768, ignore=-1, seed=0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(N, H, generator=g).to(dtype)
+    W = (torch.randn(H, V, generator=g) / H ** 0.5).to(dtype)
+    y = torch.randint(0, V, (N,), generator=g)
+    y[torch.rand(N, generator=g) < 0.1] = ignore
+    return x, y, W
+
+
+def test_product_path_refuses_cpu_tensors():
+    ops.set_backend(None)
+    x, y, W = make()
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        linear_cross_entropy(x.requires_grad_(True), y, W)
+
+
+@pytest.mark.parametrize("chunk", [128, 256, 4096])
+def test_chunk_loop_matches_oracle(fake, chunk):
+    x, y, W = make()
+    x.requires_grad_(True)
+    W.requires_grad_(True)
+    out = linear_cross_entropy(x, y, W, ignore_index=-1, z_regularization=1e-3, logit_scale=0.7, N_chunk_size=chunk,
+                               monitoring=True)
+    out[0].backward()
+    ref = oracle.forward_backward(x, y, W, -1, 1e-3, 0.7)
+    got = [v.item() for v in out]
+    np.testing.assert_allclose(got, [ref.loss, ref.z_value, ref.logit_max, ref.logit_entropy, ref.logit_norm], rtol=2e-6)
+    np.testing.assert_allclose(x.grad.numpy(), ref.dx, atol=1e-7)
+    np.testing.assert_allclose(W.grad.numpy(), ref.dW, atol=1e-7)
+    n_chunks = -(-512 // min(512, chunk))
+    assert fake.calls.count("forward_chunk") == n_chunks == fake.calls.count("backward_chunk")
+    assert fake.calls[0] == "begin" and "finalize" in fake.calls
+
+
+def test_grad_output_scales_both_gradients(fake):
+    x, y, W = make(seed=1)
+    x.requires_grad_(True)
+    W.requires_grad_(True)
+    loss = linear_cross_entropy(x, y, W, ignore_index=-1)[0]
+    (3.0 * loss).backward()
+    ref = oracle.forward_backward(x, y, W, -1)
+    np.testing.assert_allclose(x.grad.numpy(), 3 * ref.dx, atol=3e-7)
+    np.testing.assert_allclose(W.grad.numpy(), 3 * ref.dW, atol=3e-7)
+
+
+def test_no_gradient_work_without_requires_grad(fake):
+    x, y, W = make(seed=2)
+    out = linear_cross_entropy(x, y, W, ignore_index=-1)
+    assert "backward_chunk" not in fake.calls
+    assert not out[0].requires_grad
+    assert abs(out[0].item() - oracle.forward_backward(x, y, W, -1, want_grad=False).loss) < 1e-5
+
+
+def test_leading_dimensions_are_flattened_and_grad_keeps_the_input_shape(fake):
+    x, y, W = make(N=512)
+    x3 = x.view(4, 128, 256).clone().requires_grad_(True)
+    loss = linear_cross_entropy(x3, y.view(4, 128), W.requires_grad_(True), ignore_index=-1)[0]
+    loss.backward()
+    assert x3.grad.shape == (4, 128, 256)
+
+
+def test_non_contiguous_inputs_are_accepted(fake):
+    x, y, W = make()
+    xs = torch.randn(512, 512)[:, ::2]  # inner stride 2 -> copied
+    Wt = W.t().contiguous().t()          # (H, V) view with V stride != 1 -> copied
+    out = linear_cross_entropy(xs.requires_grad_(True), y, Wt.requires_grad_(True), ignore_index=-1)
+    ref = oracle.forward_backward(xs, y, Wt, -1, want_grad=False)
+    assert abs(out[0].item() - ref.loss) < 1e-5
+
+
+def test_shape_and_dtype_checks(fake):
+    x, y, W = make()
+    with pytest.raises(AssertionError):
+        linear_cross_entropy(x[:100], y[:100], W)
+    with pytest.raises(AssertionError):
+        linear_cross_entropy(x, y, W[:, :100])
+    with pytest.raises(AssertionError):
+        linear_cross_entropy(x, y.int(), W)
+    with pytest.raises(AssertionError):
+        linear_cross_entropy(x, y, W.half())
+    with pytest.raises(AssertionError):
+        linear_cross_entropy(x, y, W, N_chunk_size=100)
+
+
+def test_module_surface_matches_the_reference(fake):
+    m = LinearCrossEntropyLoss(256, 768, ignore_index=-1, logit_scale=0.5, z_regularization=1e-4, N_chunk_size=256)
+    assert isinstance(m, torch.nn.Linear)
+    assert list(m.state_dict().keys()) == ["weight"]
+    assert m.weight.shape == (256, 768)          # transposed with respect to nn.Linear
+    assert not hasattr(m, "bias") or m.__dict__.get("bias") is None
+    assert m.monitoring is False and m.latest_metrics == {}
+    assert m.weight.abs().max().item() <= 3 / 256 ** 0.5 + 1e-6
+    assert "bias=False" in repr(m)
+    x, y, _ = make()
+    loss = m(x, y)
+    assert loss.dim() == 0 and loss.dtype == torch.float32
+    assert m.latest_metrics == {}
+    m.monitoring = True
+    loss = m(x, y)
+    assert set(m.latest_metrics) == {"logit_norm", "logit_max", "logit_entropy", "z_value"}
+    loss.backward()
+    ref = oracle.forward_backward(x, y, m.weight, -1, 1e-4, 0.5)
+    np.testing.assert_allclose(m.weight.grad.numpy(), ref.dW, atol=1e-7)
+
+
+def test_module_constructor_asserts():
+    for bad in [dict(in_features=100), dict(out_features=1000), dict(N_chunk_size=100), dict(logit_scale=0.0),
+                dict(z_regularization=-1.0)]:
+        kw = dict(in_features=256, out_features=512)
+        kw.update(bad)
+        with pytest.raises(AssertionError):
+            LinearCrossEntropyLoss(**kw)
+
+
+def test_custom_init_method_is_used():
+    m = LinearCrossEntropyLoss(256, 512, init_method=lambda w: torch.nn.init.constant_(w, 0.25))
+    assert torch.all(m.weight == 0.25)
+
+
+def test_export_names_of_the_reference_package():
+    import linear_cross_entropy_loss_b200 as pkg
+
+    for name in ["fwd_configs", "bwd_configs", "LinearCrossEntropyLoss", "linear_cross_entropy"]:
+        assert hasattr(pkg, name)
