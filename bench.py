@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--config", default="headline_bf16")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--gemm-variant", type=int, default=0, choices=[0, 1],
+                    help="0: CTA-pair tensor-core kernels (default), 1: single-CTA kernels (A/B measurement)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1, rank 0)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU work of the baseline leg")
     ap.add_argument("--ref-budget", type=float, default=100.0,
@@ -188,6 +190,7 @@ def config_dict(cfg, n_gpus, args):
         "N": cfg.N, "H": cfg.H, "V": cfg.V, "N_chunk_size": cfg.N_chunk_size,
         "vocab_sharding": f"{n_gpus} x {cfg.V // n_gpus} columns" if n_gpus > 1 else "none",
         "l2": "inputs larger than L2 (the weight alone is >= 512 MiB per GPU); no explicit flush",
+        "gemm_variant": "single-CTA 128x256 tiles" if getattr(args, "gemm_variant", 0) == 1 else "CTA-pair 256x256 tiles",
     }
 
 
@@ -227,6 +230,7 @@ def main():
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    _native.check(_native.load().lce_set_gemm_variant(args.gemm_variant), "lce_set_gemm_variant")
     sharded = world > 1
     if sharded:
         dist.init_process_group("nccl", device_id=dev)
@@ -314,13 +318,16 @@ def main():
     # ---- roofline of the dominant kernel --------------------------------------------------------------
     peaks, peak_source = load_peaks()
     peak_tflops = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
-    per_launch_flops = 2.0 * min(cfg.N, cfg.N_chunk_size) * cfg.H * v_local   # one contraction over one row chunk
+    # each of the three contractions does 2*N*H*V_local flop per step, spread over its launches of that step
+    per_step_flops = 2.0 * cfg.N * cfg.H * v_local
     kernels = {}
     for k in ("fwd", "dx", "dw"):
         if kernel_launches[k] > 0:
+            per_step = kernel_launches[k] / args.steps
             avg_ms = kernel_ms[k] / kernel_launches[k]
-            kernels[k] = {"launches_per_step": kernel_launches[k] / args.steps, "avg_ms": avg_ms,
-                          "tflops": per_launch_flops / (avg_ms * 1e-3) / 1e12,
+            kernels[k] = {"launches_per_step": per_step, "avg_ms": avg_ms,
+                          "flops_per_launch": per_step_flops / per_step,
+                          "tflops": per_step_flops / per_step / (avg_ms * 1e-3) / 1e12,
                           "share_of_step": kernel_ms[k] / (ms_per_step * args.steps)}
     dominant = max(kernels, key=lambda k: kernels[k]["avg_ms"] * kernels[k]["launches_per_step"]) if kernels else None
     roofline = None
@@ -330,7 +337,7 @@ def main():
                     "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved / peak_tflops,
                     "peak_source": f"{peak_source} cuBLAS bf16 GEMM, sustained",
                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(dominant),
-                    "flops_per_launch": per_launch_flops, "kernels": kernels,
+                    "flops_per_launch": kernels[dominant]["flops_per_launch"], "kernels": kernels,
                     "whole_step_frac": (value / world) / peak_tflops}
 
     line = {

@@ -84,13 +84,15 @@ int lce_workspace_bytes(const lce_problem* p, size_t* bytes);
  *   [sharded: all-gather the row partials of all ranks]
  *   lce_combine_chunk             log-sum-exp per row, loss / metric sums (ops.py:753-761)
  *   lce_backward_chunk            dZ, dx rows of the chunk, dW accumulation (ops.py:763-791)
+ *                                 (= lce_dz_chunk + lce_dx_chunk + lce_dw_chunk)
  *   [sharded: all-reduce the chunk's dx rows]
  * lce_finalize         once:      5 scalars (ops.py:793-802)
  */
 int lce_begin(const lce_problem* p, const int64_t* labels, void* workspace, void* stream);
 
 /* x: [n_rows_total, hidden] with row stride x_ld elements; weight: [hidden, vocab_local] with row
- * stride w_ld elements; labels: [n_rows_total]. Processes rows [row0, row0 + rows).
+ * stride w_ld elements; labels: [n_rows_total]. Processes rows [row0, row0 + rows), which must lie
+ * inside one chunk (chunks start at multiples of chunk_rows) and be 128-aligned.
  * row_parts_local: float[LCE_ROW_PARTS * chunk_rows] output (this rank's per-row partials). */
 int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
                       const int64_t* labels, int64_t row0, int64_t rows, void* workspace,
@@ -101,14 +103,32 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
 int lce_combine_chunk(const lce_problem* p, const float* row_parts_all, const int64_t* labels, int64_t row0,
                       int64_t rows, void* workspace, void* stream);
 
-/* dx: [n_rows_total, hidden] (row stride dx_ld, element type dx_dtype = LCE_DTYPE_*), rows
- * [row0, row0+rows) are written. dweight: float[hidden, vocab_local] (row stride dw_ld), overwritten
- * when first_chunk != 0, else accumulated into. Both gradients are those of the mean loss
- * (already multiplied by logit_scale / n_valid, ops.py:332,443). */
+/* The backward half of a chunk, in three steps that may also be called one by one (each on rows
+ * [row0, row0 + rows) of one chunk; a call may cover a 128-aligned part of a chunk, which is how the
+ * host overlaps the slab transform of one half chunk with the tensor-core work of the other):
+ *
+ * lce_dz_chunk   turns the slab rows from exp(z - tile max) into dZ = softmax*(1 + 2 z_reg lse) - onehot
+ *                in place (ops.py:309-314). Needs lce_combine_chunk of the same rows.
+ * lce_dx_chunk   dx rows = dZ W^T * logit_scale / n_valid (ops.py:317,332). dx: [n_rows_total, hidden]
+ *                with row stride dx_ld and element type dx_dtype (LCE_DTYPE_*).
+ * lce_dw_chunk   dW (+)= x^T dZ * logit_scale / n_valid (ops.py:424,443) accumulated in fp32:
+ *                dweight_acc float[hidden, vocab_local] (row stride dw_ld) is overwritten when first != 0
+ *                and accumulated into otherwise. When dweight_final is non-null this call is the last of
+ *                the pass: the finished sum is written there in the element type of x / W (row stride
+ *                dwf_ld) and dweight_acc is only read. A pass of a single call (first != 0 and dweight_final
+ *                given) needs no dweight_acc at all (may be null).
+ * lce_backward_chunk = the three in sequence. */
+int lce_dz_chunk(const lce_problem* p, const int64_t* labels, int64_t row0, int64_t rows, void* workspace,
+                 void* stream);
+int lce_dx_chunk(const lce_problem* p, const void* weight, int64_t w_ld, int64_t row0, int64_t rows, void* workspace,
+                 void* dx, int64_t dx_ld, int32_t dx_dtype, void* stream);
+int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0, int64_t rows, void* workspace,
+                 float* dweight_acc, int64_t dw_ld, int32_t first, void* dweight_final, int64_t dwf_ld,
+                 void* stream);
 int lce_backward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
                        const int64_t* labels, int64_t row0, int64_t rows, void* workspace, void* dx,
-                       int64_t dx_ld, int32_t dx_dtype, float* dweight, int64_t dw_ld, int32_t first_chunk,
-                       void* stream);
+                       int64_t dx_ld, int32_t dx_dtype, float* dweight_acc, int64_t dw_ld, int32_t first,
+                       void* dweight_final, int64_t dwf_ld, void* stream);
 
 /* out5: float[5] = loss, z_value, logit_max, logit_entropy, logit_norm (the reference's return
  * tuple, ops.py:802). The last three are only meaningful with monitoring. If any kernel of the pass
@@ -116,7 +136,8 @@ int lce_backward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const 
 int lce_finalize(const lce_problem* p, void* workspace, float* out5, void* stream);
 
 /* dst[r, c] = src[r, c] * (*dev_factor), converting element type (the reference's
- * x_grad.mul_(grad_output), ops.py:810). src == dst is allowed when the types match. */
+ * x_grad.mul_(grad_output), ops.py:810). cols % 8 == 0. src == dst is allowed when the types match, and
+ * then a factor of exactly 1 (the plain loss.backward() case) leaves the data untouched. */
 int lce_grad_scale_cast(const void* src, int32_t src_dtype, int64_t src_ld, void* dst, int32_t dst_dtype,
                         int64_t dst_ld, int64_t rows, int64_t cols, const float* dev_factor, void* stream);
 
@@ -134,10 +155,18 @@ int lce_profile_enable(int32_t enable);
 int lce_profile_read(double* ms3, long long* launches3);
 
 /* ---- diagnostics ------------------------------------------------------------------------------
+ * lce_set_gemm_variant: 0 (default) runs the contractions on CTA pairs (cta_group::2, 256 x 256 tiles)
+ * whenever the row count allows it; 1 forces the single-CTA kernel (128 x 256 tiles) everywhere.
+ * Process-wide; for A/B measurements and tests. No counterpart in the reference. */
+int lce_set_gemm_variant(int32_t variant);
+
+/*
  * Runs the GEMM engine alone: out[s][M, N] = A * B^T over K-split s (fp32, row stride N).
  * a_mn_major == 0: a is [M, K] (K contiguous, row stride a_ld); != 0: a is [K, M] (row stride a_ld).
  * Same for b with N. M % 128 == 0, N % 256 == 0, K % (splits * 128 bytes) == 0.
- * dev_status: int[1] device word. No counterpart in the reference. */
+ * dev_status: int[8] device words, 8-byte aligned: [0] status (0 = ok); [2..3] int64 SM cycles and [4..5] int64
+ * nanoseconds that CTA 0 spent in the kernel (their ratio is the SM clock the kernel ran at).
+ * No counterpart in the reference. */
 int lce_debug_gemm(int32_t dtype, int32_t a_mn_major, int32_t b_mn_major, const void* a, int64_t a_ld,
                    const void* b, int64_t b_ld, float* out, int64_t m, int64_t n, int64_t k, int32_t splits,
                    int* dev_status, void* stream);

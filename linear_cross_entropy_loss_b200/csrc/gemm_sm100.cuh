@@ -74,6 +74,8 @@ struct GemmParams {
   int accumulate;              // 0: out = coef * acc, 1: out += coef * acc
   float out_scale;             // coef = out_scale / (*out_div)   (out_div may be null: coef = out_scale)
   const float* out_div;
+  void* out_final;             // when non-null the result goes here, converted to the input element type,
+  long long out_final_ld;      // instead of back to `out` (last accumulation step of dW)
 
   // ---- EPI_FWD: softmax statistics + exp slab
   void* slab;                  // [rows, slab_ld] in the input element type: exp(z - tile row max)
@@ -91,6 +93,7 @@ struct GemmParams {
   float scale;                 // logit scale (> 0)
 
   int* status;                 // device status word (0 = ok)
+  long long* clock_probe;      // optional [2]: SM cycles and nanoseconds CTA 0 spent in the kernel (diagnostics)
 };
 
 // --------------------------------------------------------------------------------------------------
@@ -237,34 +240,40 @@ __device__ __forceinline__ void epilogue_forward(const GemmParams& p, uint32_t t
   if (ycol >= 0) p.target_logit[r] = tv * p.scale;
 }
 
-// Plain fp32 epilogue: out[split][row, col] (+)= coef * acc.
+// Plain fp32 epilogue: result = coef * acc (+ out[split][row, col] when accumulating); the result is stored
+// to out, or -- converted to the input element type -- to out_final when that is given.
+template <int kKind>
 __device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk, int split,
                                              int row_in_tile) {
-  float* dst = p.out + (long long)split * p.out_split_stride +
-               ((long long)m_blk * BLOCK_M + row_in_tile) * p.out_ld + (long long)n_blk * BLOCK_N;
+  using Elem = typename SlabElem<kKind>::type;
+  const long long row = (long long)m_blk * BLOCK_M + row_in_tile;
+  float* dst = p.out + (long long)split * p.out_split_stride + row * p.out_ld + (long long)n_blk * BLOCK_N;
+  Elem* dst_final = reinterpret_cast<Elem*>(p.out_final) + row * p.out_final_ld + (long long)n_blk * BLOCK_N;
   const float coef = (p.out_div != nullptr) ? p.out_scale / __ldg(p.out_div) : p.out_scale;
 #pragma unroll 1
   for (int c = 0; c < BLOCK_N / 32; ++c) {
     uint32_t v[32];
     tmem_ld_32x32b_x32(taddr + c * 32, v);
     tmem_ld_wait();
-    float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
+    float r[32];
     if (p.accumulate) {
+      const float4* s4 = reinterpret_cast<const float4*>(dst + c * 32);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        float4 o = d4[i];
-        o.x = fmaf(coef, __uint_as_float(v[4 * i + 0]), o.x);
-        o.y = fmaf(coef, __uint_as_float(v[4 * i + 1]), o.y);
-        o.z = fmaf(coef, __uint_as_float(v[4 * i + 2]), o.z);
-        o.w = fmaf(coef, __uint_as_float(v[4 * i + 3]), o.w);
-        d4[i] = o;
+        const float4 o = s4[i];
+        r[4 * i + 0] = fmaf(coef, __uint_as_float(v[4 * i + 0]), o.x);
+        r[4 * i + 1] = fmaf(coef, __uint_as_float(v[4 * i + 1]), o.y);
+        r[4 * i + 2] = fmaf(coef, __uint_as_float(v[4 * i + 2]), o.z);
+        r[4 * i + 3] = fmaf(coef, __uint_as_float(v[4 * i + 3]), o.w);
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        d4[i] = make_float4(coef * __uint_as_float(v[4 * i + 0]), coef * __uint_as_float(v[4 * i + 1]),
-                            coef * __uint_as_float(v[4 * i + 2]), coef * __uint_as_float(v[4 * i + 3]));
+      for (int i = 0; i < 32; ++i) r[i] = coef * __uint_as_float(v[i]);
     }
+    if (p.out_final != nullptr)
+      store_slab_chunk(dst_final + c * 32, r);
+    else
+      store_slab_chunk(dst + c * 32, r);
   }
 }
 
@@ -317,6 +326,11 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sh->tmem_base;
+  long long probe_c0 = 0, probe_t0 = 0;
+  if (p.clock_probe != nullptr && blockIdx.x == 0 && threadIdx.x == 64) {
+    probe_c0 = clock64();
+    probe_t0 = (long long)global_timer_ns();
+  }
 
   const int units = p.splits * p.n_tiles * p.m_tiles;
   const int tiles_mn = p.n_tiles * p.m_tiles;
@@ -423,7 +437,7 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int rem = unit - split * tiles_mn;
       const int n_blk = rem / p.m_tiles;
       const int m_blk = rem - n_blk * p.m_tiles;
-      if (!mbar_wait(&sh->acc_full[acc], acc_phase, abort_flag)) {
+      if (!mbar_wait_warp(&sh->acc_full[acc], acc_phase, abort_flag)) {
         if (lane == 0) atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_EPILOGUE);
         break;
       }
@@ -432,7 +446,7 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (kEpi == EPI_FWD)
         epilogue_forward<kKind, kMonitor>(p, taddr, m_blk, n_blk, row_in_tile);
       else
-        epilogue_f32(p, taddr, m_blk, n_blk, split, row_in_tile);
+        epilogue_f32<kKind>(p, taddr, m_blk, n_blk, split, row_in_tile);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
@@ -444,6 +458,10 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
 
   // ------------------------------------------------------------------ teardown
+  if (p.clock_probe != nullptr && blockIdx.x == 0 && threadIdx.x == 64) {
+    p.clock_probe[0] = clock64() - probe_c0;
+    p.clock_probe[1] = (long long)global_timer_ns() - probe_t0;
+  }
   if (*abort_flag != 0) {
     // a wait ran out: give copies that may still be in flight time to land before smem goes away
     for (int i = 0; i < 64; ++i) __nanosleep(10000);
@@ -454,6 +472,250 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// --------------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2): two CTAs of a cluster share one 256 x 256 output tile.
+//
+// CTA r of the pair owns accumulator rows [128 r, 128 r + 128) of the tile in its own TMEM, loads the
+// matching 128 rows of A and columns [128 r, 128 r + 128) of B into its own shared memory, and runs its
+// own epilogue; CTA 0 alone issues the MMAs, which read both CTAs' operand tiles. Per K-block each SM
+// therefore stages and reads 32 KiB instead of 48 KiB, which is what lets the tensor pipes run closer
+// to their peak under the chip's power limit.
+//
+// Barriers: every TMA load of either CTA counts its bytes on CTA 0's full[stage]; CTA 0 commits each
+// MMA batch to empty[stage] of BOTH CTAs and each finished accumulator to acc_full of both; the epilogue
+// warps of both CTAs arrive on CTA 0's acc_empty (8 arrivals).
+// --------------------------------------------------------------------------------------------------
+#ifndef LCE_PAIR_STAGES
+#define LCE_PAIR_STAGES 6
+#endif
+constexpr int kPairStages = LCE_PAIR_STAGES;
+constexpr int kPairBTileBytes = (BLOCK_N / 2) * 128;  // 16 KiB: this CTA's half of the B tile
+constexpr int kPairStageBytes = kATileBytes + kPairBTileBytes;
+constexpr int PAIR_M = 2 * BLOCK_M;
+
+struct GemmPairShared {
+  uint64_t full[kPairStages];
+  uint64_t empty[kPairStages];
+  uint64_t acc_full[kAccStages];
+  uint64_t acc_empty[kAccStages];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr size_t kGemmPairSmemBytes = size_t(kPairStages) * kPairStageBytes + 1024 + sizeof(GemmPairShared);
+
+template <int kKind, bool kAMN, bool kBMN>
+__host__ __device__ constexpr uint32_t make_instr_desc_pair() {
+  const uint32_t fmt = (kKind == KIND_F16) ? 0u : (kKind == KIND_BF16 ? 1u : 2u);
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((kAMN ? 1u : 0u) << 15) | ((kBMN ? 1u : 0u) << 16) |
+         (uint32_t(BLOCK_N >> 3) << 17) | (uint32_t(PAIR_M >> 4) << 24);
+}
+
+// p.m_tiles counts 256-row tiles here.
+template <int kKind, bool kAMN, bool kBMN, int kEpi, bool kMonitor>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const GemmParams p) {
+  constexpr int ES = (kKind == KIND_TF32) ? 4 : 2;
+  constexpr int BLOCK_K = 128 / ES;
+  constexpr int UMMA_K = 32 / ES;
+  constexpr int MN_BOX = 128 / ES;
+  constexpr int K_STEPS = BLOCK_K / UMMA_K;
+  constexpr uint32_t kAdvA = kAMN ? (UMMA_K * 128) >> 4 : 32 >> 4;
+  constexpr uint32_t kAdvB = kBMN ? (UMMA_K * 128) >> 4 : 32 >> 4;
+  constexpr uint32_t kIdesc = make_instr_desc_pair<kKind, kAMN, kBMN>();
+  constexpr int HALF_N = BLOCK_N / 2;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  GemmPairShared* sh = reinterpret_cast<GemmPairShared*>(tiles + size_t(kPairStages) * kPairStageBytes);
+  volatile int* abort_flag = &sh->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = (rank == 0);
+  const int cluster_id = blockIdx.x >> 1;
+  const int n_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&sh->full[s], 1);   // used in CTA 0 only: one expect_tx arrival + the bytes of both CTAs
+      mbar_init(&sh->empty[s], 1);  // one commit from CTA 0
+    }
+    for (int a = 0; a < kAccStages; ++a) {
+      mbar_init(&sh->acc_full[a], 1);
+      mbar_init(&sh->acc_empty[a], 8);  // used in CTA 0 only: 4 epilogue warps of each CTA
+    }
+    sh->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&sh->tmem_base, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();  // both CTAs' barriers are initialised and both allocations are done
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sh->tmem_base;
+  long long probe_c0 = 0, probe_t0 = 0;
+  if (p.clock_probe != nullptr && blockIdx.x == 0 && threadIdx.x == 64) {
+    probe_c0 = clock64();
+    probe_t0 = (long long)global_timer_ns();
+  }
+
+  const int units = p.splits * p.n_tiles * p.m_tiles;
+  const int tiles_mn = p.n_tiles * p.m_tiles;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = cluster_id; ok && unit < units; unit += n_clusters) {
+        const int split = unit / tiles_mn;
+        const int rem = unit - split * tiles_mn;
+        const int n_blk = rem / p.m_tiles;
+        const int m_blk = rem - n_blk * p.m_tiles;
+        const int a_mn = p.a_mn0 + m_blk * PAIR_M + int(rank) * BLOCK_M;
+        const int b_mn = p.b_mn0 + n_blk * BLOCK_N + int(rank) * HALF_N;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) {
+            atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          uint8_t* sA = tiles + size_t(stage) * kPairStageBytes;
+          uint8_t* sB = sA + kATileBytes;
+          const int kc = (split * p.k_blocks + kb) * BLOCK_K;
+          if (leader) mbar_arrive_expect_tx(&sh->full[stage], 2 * kPairStageBytes);
+          const uint32_t full0 = map_to_cta(smem_u32(&sh->full[stage]), 0);
+          if (!kAMN) {
+            tma_load_2d_pair(sA, &tmA, full0, p.a_k0 + kc, a_mn);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_M / MN_BOX; ++j)
+              tma_load_2d_pair(sA + j * (BLOCK_K * 128), &tmA, full0, a_mn + j * MN_BOX, p.a_k0 + kc);
+          }
+          if (!kBMN) {
+            tma_load_2d_pair(sB, &tmB, full0, p.b_k0 + kc, b_mn);
+          } else {
+#pragma unroll
+            for (int j = 0; j < HALF_N / MN_BOX; ++j)
+              tma_load_2d_pair(sB + j * (BLOCK_K * 128), &tmB, full0, b_mn + j * MN_BOX, p.b_k0 + kc);
+          }
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (CTA 0 only)
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int unit = cluster_id; ok && unit < units; unit += n_clusters) {
+        if (!mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
+          atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_MMA);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + uint32_t(acc * BLOCK_N);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&sh->full[stage], phase, abort_flag)) {
+            atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sA = smem_u32(tiles + size_t(stage) * kPairStageBytes);
+          const uint64_t adesc = make_smem_desc<kAMN, BLOCK_K, kAMN && kKind == KIND_TF32>(sA);
+          const uint64_t bdesc = make_smem_desc<kBMN, BLOCK_K, kBMN && kKind == KIND_TF32>(sA + kATileBytes);
+#pragma unroll
+          for (int k = 0; k < K_STEPS; ++k) {
+            const uint32_t accum = (kb | k) != 0 ? 1u : 0u;
+            if (kKind == KIND_TF32)
+              umma_pair_tf32(d_tmem, adesc + uint64_t(k * kAdvA), bdesc + uint64_t(k * kAdvB), kIdesc, accum);
+            else
+              umma_pair_f16(d_tmem, adesc + uint64_t(k * kAdvA), bdesc + uint64_t(k * kAdvB), kIdesc, accum);
+          }
+          const uint32_t e_local = smem_u32(&sh->empty[stage]);
+          umma_pair_commit(e_local);                 // frees this stage in CTA 0 ...
+          umma_pair_commit(map_to_cta(e_local, 1));  // ... and in CTA 1
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        const uint32_t f_local = smem_u32(&sh->acc_full[acc]);
+        umma_pair_commit(f_local);
+        umma_pair_commit(map_to_cta(f_local, 1));
+        if (++acc == kAccStages) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (both CTAs)
+    const int lane_group = warp & 3;
+    const int row_in_tile = lane_group * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int unit = cluster_id; unit < units; unit += n_clusters) {
+      const int split = unit / tiles_mn;
+      const int rem = unit - split * tiles_mn;
+      const int n_blk = rem / p.m_tiles;
+      const int m_blk = rem - n_blk * p.m_tiles;
+      const int m_blk128 = m_blk * 2 + int(rank);  // this CTA's 128-row block
+      if (!mbar_wait_warp(&sh->acc_full[acc], acc_phase, abort_flag)) {
+        if (lane == 0) atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_EPILOGUE);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + uint32_t(acc * BLOCK_N);
+      if (kEpi == EPI_FWD)
+        epilogue_forward<kKind, kMonitor>(p, taddr, m_blk128, n_blk, row_in_tile);
+      else
+        epilogue_f32<kKind>(p, taddr, m_blk128, n_blk, split, row_in_tile);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&sh->acc_empty[acc]), 0));
+      if (++acc == kAccStages) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (p.clock_probe != nullptr && blockIdx.x == 0 && threadIdx.x == 64) {
+    p.clock_probe[0] = clock64() - probe_c0;
+    p.clock_probe[1] = (long long)global_timer_ns() - probe_t0;
+  }
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+  }
+  tc_fence_before_sync();
+  __syncwarp();
+  cluster_sync_all();  // neither CTA may leave while the peer can still touch its shared memory or TMEM
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 

@@ -16,6 +16,8 @@ namespace {
 using namespace lce;
 
 std::atomic<long long> g_launches{0};
+// 0: CTA-pair kernel whenever the tile grid allows it, 1: always the single-CTA kernel (lce_set_gemm_variant)
+std::atomic<int> g_gemm_variant{0};
 
 // ------------------------------------------------------------------------------------------------
 // device bookkeeping
@@ -32,8 +34,11 @@ EncodeTiledFn g_encode = nullptr;
 
 template <int kKind, bool kAMN, bool kBMN, int kEpi, bool kMon>
 cudaError_t set_smem_attr() {
-  return cudaFuncSetAttribute(lce_gemm_kernel<kKind, kAMN, kBMN, kEpi, kMon>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(lce_gemm_kernel<kKind, kAMN, kBMN, kEpi, kMon>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(lce_gemm_pair_kernel<kKind, kAMN, kBMN, kEpi, kMon>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmPairSmemBytes);
 }
 
 template <int kKind>
@@ -252,28 +257,50 @@ struct ProfScope {
   }
 };
 
+// With an even number of 128-row tiles (and at least two SMs) a contraction runs on the CTA-pair kernel:
+// 256 x 256 tiles, one per cluster of two CTAs, each CTA loading 128 rows of A and 128 of the 256 B columns.
+// The B tensor map must be built for the variant that will run (rows_of_b_tile).
+bool use_pair_kernel(long long m_tiles128, int sms) {
+  return (m_tiles128 % 2 == 0) && sms >= 2 && g_gemm_variant.load(std::memory_order_relaxed) == 0;
+}
+int rows_of_b_tile(bool pair) { return pair ? BLOCK_N / 2 : BLOCK_N; }
+
+// gp.m_tiles counts 128-row tiles; `pair` must be the value the tensor maps were built for.
 template <int kKind, bool kAMN, bool kBMN, int kEpi, bool kMon>
-int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& gp, int sms, cudaStream_t st) {
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& gp_in, int sms, cudaStream_t st,
+                bool pair) {
+  GemmParams gp = gp_in;
+  if (pair && gp.m_tiles % 2 != 0) return LCE_ERR_INVALID_ARGUMENT;
+  if (pair) gp.m_tiles /= 2;
   const long long units = (long long)gp.splits * gp.n_tiles * gp.m_tiles;
   if (units <= 0 || units > (1ll << 30)) return LCE_ERR_TOO_LARGE;
-  const int grid = (int)(units < sms ? units : sms);
-  lce_gemm_kernel<kKind, kAMN, kBMN, kEpi, kMon><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(ta, tb, gp);
+  if (pair) {
+    const long long clusters = units < sms / 2 ? units : sms / 2;
+    lce_gemm_pair_kernel<kKind, kAMN, kBMN, kEpi, kMon>
+        <<<(int)(2 * clusters), kGemmThreads, kGemmPairSmemBytes, st>>>(ta, tb, gp);
+  } else {
+    const int grid = (int)(units < sms ? units : sms);
+    lce_gemm_kernel<kKind, kAMN, kBMN, kEpi, kMon><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(ta, tb, gp);
+  }
   return check_launch();
 }
 
 template <bool kAMN, bool kBMN, int kEpi, bool kMon>
 int launch_gemm_dtype(int dtype, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& gp, int sms,
-                      cudaStream_t st) {
+                      cudaStream_t st, bool pair) {
   switch (dtype) {
-    case LCE_DTYPE_F16: return launch_gemm<KIND_F16, kAMN, kBMN, kEpi, kMon>(ta, tb, gp, sms, st);
-    case LCE_DTYPE_BF16: return launch_gemm<KIND_BF16, kAMN, kBMN, kEpi, kMon>(ta, tb, gp, sms, st);
-    case LCE_DTYPE_F32: return launch_gemm<KIND_TF32, kAMN, kBMN, kEpi, kMon>(ta, tb, gp, sms, st);
+    case LCE_DTYPE_F16: return launch_gemm<KIND_F16, kAMN, kBMN, kEpi, kMon>(ta, tb, gp, sms, st, pair);
+    case LCE_DTYPE_BF16: return launch_gemm<KIND_BF16, kAMN, kBMN, kEpi, kMon>(ta, tb, gp, sms, st, pair);
+    case LCE_DTYPE_F32: return launch_gemm<KIND_TF32, kAMN, kBMN, kEpi, kMon>(ta, tb, gp, sms, st, pair);
   }
   return LCE_ERR_INVALID_ARGUMENT;
 }
 
+// Rows [row0, row0 + rows) must lie inside ONE chunk (chunks start at multiples of chunk_rows); a call may
+// cover a whole chunk or a 128-aligned part of it.
 int check_chunk(const lce_problem* p, int64_t row0, int64_t rows) {
   if (row0 < 0 || rows <= 0 || rows > p->chunk_rows || row0 + rows > p->n_rows_total) return LCE_ERR_INVALID_ARGUMENT;
+  if (row0 % p->chunk_rows + rows > p->chunk_rows) return LCE_ERR_INVALID_ARGUMENT;
   if (rows % BLOCK_M != 0 || row0 % BLOCK_M != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
   return LCE_OK;
 }
@@ -347,10 +374,13 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
   cudaStream_t st = (cudaStream_t)stream;
   const Workspace w = layout_workspace(p, workspace, sms);
   const int es = elem_size(p->dtype);
+  const long long local0 = row0 % p->chunk_rows;  // first row inside the chunk's slab and statistics
 
+  const bool pair = use_pair_kernel(rows / BLOCK_M, sms);
   CUtensorMap ta, tb;
   if ((v = make_operand_tmap(&ta, p->dtype, false, x, p->hidden, p->n_rows_total, x_ld, BLOCK_M)) != LCE_OK) return v;
-  if ((v = make_operand_tmap(&tb, p->dtype, true, weight, p->vocab_local, p->hidden, w_ld, BLOCK_N)) != LCE_OK)
+  if ((v = make_operand_tmap(&tb, p->dtype, true, weight, p->vocab_local, p->hidden, w_ld, rows_of_b_tile(pair))) !=
+      LCE_OK)
     return v;
 
   GemmParams gp;
@@ -360,15 +390,15 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
   gp.splits = 1;
   gp.k_blocks = (int)(p->hidden * es / 128);
   gp.a_mn0 = (int)row0;
-  gp.slab = w.slab;
+  gp.slab = w.slab ? reinterpret_cast<char*>(w.slab) + (size_t)local0 * (size_t)p->vocab_local * es : nullptr;
   gp.slab_ld = p->vocab_local;
   gp.store_slab = (p->want_grad && w.slab != nullptr) ? 1 : 0;
-  gp.tile_max = w.tile_max;
-  gp.tile_sum = w.tile_sum;
-  gp.tile_ez = w.tile_ez;
-  gp.tile_sq = w.tile_sq;
+  gp.tile_max = w.tile_max + local0;
+  gp.tile_sum = w.tile_sum + local0;
+  gp.tile_ez = w.tile_ez + local0;
+  gp.tile_sq = w.tile_sq + local0;
   gp.stat_ld = p->chunk_rows;
-  gp.target_logit = w.target_logit;
+  gp.target_logit = w.target_logit + local0;
   gp.labels = reinterpret_cast<const long long*>(labels) + row0;
   gp.ignore_index = p->ignore_index;
   gp.vocab_offset = p->vocab_offset;
@@ -377,21 +407,21 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
 
   {
     ProfScope prof(PROF_FWD, st);
-    v = p->monitoring ? launch_gemm_dtype<false, true, EPI_FWD, true>(p->dtype, ta, tb, gp, sms, st)
-                      : launch_gemm_dtype<false, true, EPI_FWD, false>(p->dtype, ta, tb, gp, sms, st);
+    v = p->monitoring ? launch_gemm_dtype<false, true, EPI_FWD, true>(p->dtype, ta, tb, gp, sms, st, pair)
+                      : launch_gemm_dtype<false, true, EPI_FWD, false>(p->dtype, ta, tb, gp, sms, st, pair);
   }
   if (v != LCE_OK) return v;
 
   const int blocks = (int)((rows + 31) / 32);
   const long long* lab = reinterpret_cast<const long long*>(labels) + row0;
   if (p->monitoring)
-    row_stats_kernel<true><<<blocks, 256, 0, st>>>(w.tile_max, w.tile_sum, w.tile_ez, w.tile_sq, w.target_logit, lab,
-                                                   (int)rows, gp.n_tiles, p->chunk_rows, p->ignore_index,
-                                                   p->vocab_offset, p->vocab_local, row_parts_local);
+    row_stats_kernel<true><<<blocks, 256, 0, st>>>(gp.tile_max, gp.tile_sum, gp.tile_ez, gp.tile_sq, gp.target_logit,
+                                                   lab, (int)rows, gp.n_tiles, p->chunk_rows, p->ignore_index,
+                                                   p->vocab_offset, p->vocab_local, row_parts_local + local0);
   else
-    row_stats_kernel<false><<<blocks, 256, 0, st>>>(w.tile_max, w.tile_sum, w.tile_ez, w.tile_sq, w.target_logit,
+    row_stats_kernel<false><<<blocks, 256, 0, st>>>(gp.tile_max, gp.tile_sum, gp.tile_ez, gp.tile_sq, gp.target_logit,
                                                     lab, (int)rows, gp.n_tiles, p->chunk_rows, p->ignore_index,
-                                                    p->vocab_offset, p->vocab_local, row_parts_local);
+                                                    p->vocab_offset, p->vocab_local, row_parts_local + local0);
   return check_launch();
 }
 
@@ -404,132 +434,181 @@ int lce_combine_chunk(const lce_problem* p, const float* row_parts_all, const in
   int sms = 0;
   if ((v = ensure_device(&sms)) != LCE_OK) return v;
   const Workspace w = layout_workspace(p, workspace, sms);
-  combine_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(row_parts_all, p->world,
+  const long long local0 = row0 % p->chunk_rows;
+  combine_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(row_parts_all + local0, p->world,
                                                        reinterpret_cast<const long long*>(labels) + row0, (int)rows,
-                                                       p->chunk_rows, p->ignore_index, p->monitoring, w.lse,
+                                                       p->chunk_rows, p->ignore_index, p->monitoring, w.lse + local0,
                                                        w.scalars);
   return check_launch();
 }
 
-int lce_backward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
-                       const int64_t* labels, int64_t row0, int64_t rows, void* workspace, void* dx, int64_t dx_ld,
-                       int32_t dx_dtype, float* dweight, int64_t dw_ld, int32_t first_chunk, void* stream) {
+int lce_dz_chunk(const lce_problem* p, const int64_t* labels, int64_t row0, int64_t rows, void* workspace,
+                 void* stream) {
   int v = validate_problem(p);
   if (v != LCE_OK) return v;
   if ((v = check_chunk(p, row0, rows)) != LCE_OK) return v;
-  if (!p->want_grad) return LCE_ERR_INVALID_ARGUMENT;
-  if (!x || !weight || !labels || !workspace || !dx || !dweight) return LCE_ERR_INVALID_ARGUMENT;
-  if (x_ld < p->hidden || w_ld < p->vocab_local || dx_ld < p->hidden || dw_ld < p->vocab_local)
-    return LCE_ERR_INVALID_ARGUMENT;
-  if (dx_dtype != LCE_DTYPE_F16 && dx_dtype != LCE_DTYPE_BF16 && dx_dtype != LCE_DTYPE_F32)
-    return LCE_ERR_INVALID_ARGUMENT;
-  if ((reinterpret_cast<uintptr_t>(dweight) & 15u) != 0 || (dw_ld & 3) != 0) return LCE_ERR_MISALIGNED;
+  if (!p->want_grad || !labels || !workspace) return LCE_ERR_INVALID_ARGUMENT;
   int sms = 0;
   if ((v = ensure_device(&sms)) != LCE_OK) return v;
   cudaStream_t st = (cudaStream_t)stream;
   const Workspace w = layout_workspace(p, workspace, sms);
   const int es = elem_size(p->dtype);
   const int n_vtiles = (int)(p->vocab_local / BLOCK_N);
+  const long long local0 = row0 % p->chunk_rows;
   const long long* lab = reinterpret_cast<const long long*>(labels) + row0;
-
-  // ---- dZ, in place on the slab
-  {
-    const long long items = (rows / 8) * n_vtiles;
-    const int grid = grid_for(items, 1, sms, 16);
-    switch (p->dtype) {
-      case LCE_DTYPE_F16:
-        dz_transform_kernel<__half><<<grid, 256, 0, st>>>(reinterpret_cast<__half*>(w.slab), p->vocab_local,
-                                                          w.tile_max, w.lse, lab, (int)rows, n_vtiles, p->chunk_rows,
-                                                          p->ignore_index, p->vocab_offset, p->z_regularization);
-        break;
-      case LCE_DTYPE_BF16:
-        dz_transform_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-            reinterpret_cast<__nv_bfloat16*>(w.slab), p->vocab_local, w.tile_max, w.lse, lab, (int)rows, n_vtiles,
-            p->chunk_rows, p->ignore_index, p->vocab_offset, p->z_regularization);
-        break;
-      default:
-        dz_transform_kernel<float><<<grid, 256, 0, st>>>(reinterpret_cast<float*>(w.slab), p->vocab_local,
-                                                         w.tile_max, w.lse, lab, (int)rows, n_vtiles, p->chunk_rows,
-                                                         p->ignore_index, p->vocab_offset, p->z_regularization);
-    }
-    if ((v = check_launch()) != LCE_OK) return v;
+  char* slab = reinterpret_cast<char*>(w.slab) + (size_t)local0 * (size_t)p->vocab_local * es;
+  const long long items = (rows / 8) * n_vtiles;
+  const int grid = grid_for(items, 1, sms, 16);
+  switch (p->dtype) {
+    case LCE_DTYPE_F16:
+      dz_transform_kernel<__half><<<grid, 256, 0, st>>>(reinterpret_cast<__half*>(slab), p->vocab_local,
+                                                        w.tile_max + local0, w.lse + local0, lab, (int)rows, n_vtiles,
+                                                        p->chunk_rows, p->ignore_index, p->vocab_offset,
+                                                        p->z_regularization);
+      break;
+    case LCE_DTYPE_BF16:
+      dz_transform_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+          reinterpret_cast<__nv_bfloat16*>(slab), p->vocab_local, w.tile_max + local0, w.lse + local0, lab, (int)rows,
+          n_vtiles, p->chunk_rows, p->ignore_index, p->vocab_offset, p->z_regularization);
+      break;
+    default:
+      dz_transform_kernel<float><<<grid, 256, 0, st>>>(reinterpret_cast<float*>(slab), p->vocab_local,
+                                                       w.tile_max + local0, w.lse + local0, lab, (int)rows, n_vtiles,
+                                                       p->chunk_rows, p->ignore_index, p->vocab_offset,
+                                                       p->z_regularization);
   }
+  return check_launch();
+}
 
+int lce_dx_chunk(const lce_problem* p, const void* weight, int64_t w_ld, int64_t row0, int64_t rows, void* workspace,
+                 void* dx, int64_t dx_ld, int32_t dx_dtype, void* stream) {
+  int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if ((v = check_chunk(p, row0, rows)) != LCE_OK) return v;
+  if (!p->want_grad || !weight || !workspace || !dx) return LCE_ERR_INVALID_ARGUMENT;
+  if (w_ld < p->vocab_local || dx_ld < p->hidden) return LCE_ERR_INVALID_ARGUMENT;
+  if (dx_dtype != LCE_DTYPE_F16 && dx_dtype != LCE_DTYPE_BF16 && dx_dtype != LCE_DTYPE_F32)
+    return LCE_ERR_INVALID_ARGUMENT;
+  int sms = 0;
+  if ((v = ensure_device(&sms)) != LCE_OK) return v;
+  cudaStream_t st = (cudaStream_t)stream;
+  const Workspace w = layout_workspace(p, workspace, sms);
+  const int es = elem_size(p->dtype);
+  const long long local0 = row0 % p->chunk_rows;
+
+  // partials[s] = dZ * W^T over K-split s of the vocabulary, scaled by logit_scale / n_valid
+  const bool pair = use_pair_kernel(rows / BLOCK_M, sms);
   CUtensorMap ta, tb;
-  // ---- dx partials = dZ * W^T over K-splits of the vocabulary, scaled by logit_scale / n_valid
+  if ((v = make_operand_tmap(&ta, p->dtype, false, w.slab, p->vocab_local, p->chunk_rows, p->vocab_local, BLOCK_M)) !=
+      LCE_OK)
+    return v;
+  if ((v = make_operand_tmap(&tb, p->dtype, false, weight, p->vocab_local, p->hidden, w_ld, rows_of_b_tile(pair))) !=
+      LCE_OK)
+    return v;
+  float* part = w.dx_part + local0 * p->hidden;
+  GemmParams gp;
+  memset(&gp, 0, sizeof(gp));
+  gp.m_tiles = (int)(rows / BLOCK_M);
+  gp.n_tiles = (int)(p->hidden / BLOCK_N);
+  gp.splits = w.dx_splits;
+  gp.k_blocks = (int)(p->vocab_local * es / 128 / w.dx_splits);
+  gp.a_mn0 = (int)local0;
+  gp.out = part;
+  gp.out_ld = p->hidden;
+  gp.out_split_stride = (long long)p->chunk_rows * p->hidden;
+  gp.accumulate = 0;
+  gp.out_scale = p->logit_scale;
+  gp.out_div = &w.scalars->n_valid;
+  gp.status = &w.scalars->status;
   {
-    if ((v = make_operand_tmap(&ta, p->dtype, false, w.slab, p->vocab_local, p->chunk_rows, p->vocab_local,
-                               BLOCK_M)) != LCE_OK)
-      return v;
-    if ((v = make_operand_tmap(&tb, p->dtype, false, weight, p->vocab_local, p->hidden, w_ld, BLOCK_N)) != LCE_OK)
-      return v;
-    GemmParams gp;
-    memset(&gp, 0, sizeof(gp));
-    gp.m_tiles = (int)(rows / BLOCK_M);
-    gp.n_tiles = (int)(p->hidden / BLOCK_N);
-    gp.splits = w.dx_splits;
-    gp.k_blocks = (int)(p->vocab_local * es / 128 / w.dx_splits);
-    gp.out = w.dx_part;
-    gp.out_ld = p->hidden;
-    gp.out_split_stride = (long long)p->chunk_rows * p->hidden;
-    gp.accumulate = 0;
-    gp.out_scale = p->logit_scale;
-    gp.out_div = &w.scalars->n_valid;
-    gp.status = &w.scalars->status;
-    {
-      ProfScope prof(PROF_DX, st);
-      v = launch_gemm_dtype<false, false, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st);
-    }
-    if (v != LCE_OK) return v;
-
-    const long long quads = rows * (p->hidden / 4);
-    const int grid = grid_for(quads, 256, sms, 8);
-    const long long ss = (long long)p->chunk_rows * p->hidden;
-    char* dx_rows = reinterpret_cast<char*>(dx) + (size_t)row0 * (size_t)dx_ld * elem_size(dx_dtype);
-    switch (dx_dtype) {
-      case LCE_DTYPE_F16:
-        dx_reduce_kernel<__half><<<grid, 256, 0, st>>>(w.dx_part, w.dx_splits, ss, (int)rows, (int)p->hidden,
-                                                       reinterpret_cast<__half*>(dx_rows), dx_ld);
-        break;
-      case LCE_DTYPE_BF16:
-        dx_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(w.dx_part, w.dx_splits, ss, (int)rows, (int)p->hidden,
-                                                              reinterpret_cast<__nv_bfloat16*>(dx_rows), dx_ld);
-        break;
-      default:
-        dx_reduce_kernel<float><<<grid, 256, 0, st>>>(w.dx_part, w.dx_splits, ss, (int)rows, (int)p->hidden,
-                                                      reinterpret_cast<float*>(dx_rows), dx_ld);
-    }
-    if ((v = check_launch()) != LCE_OK) return v;
+    ProfScope prof(PROF_DX, st);
+    v = launch_gemm_dtype<false, false, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st, pair);
   }
+  if (v != LCE_OK) return v;
 
-  // ---- dW (+)= x^T * dZ, scaled by logit_scale / n_valid
+  // fixed-order sum of the partials -> dx rows
+  const long long quads = rows * (p->hidden / 4);
+  const int grid = grid_for(quads, 256, sms, 8);
+  const long long ss = (long long)p->chunk_rows * p->hidden;
+  char* dx_rows = reinterpret_cast<char*>(dx) + (size_t)row0 * (size_t)dx_ld * elem_size(dx_dtype);
+  switch (dx_dtype) {
+    case LCE_DTYPE_F16:
+      dx_reduce_kernel<__half><<<grid, 256, 0, st>>>(part, w.dx_splits, ss, (int)rows, (int)p->hidden,
+                                                     reinterpret_cast<__half*>(dx_rows), dx_ld);
+      break;
+    case LCE_DTYPE_BF16:
+      dx_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(part, w.dx_splits, ss, (int)rows, (int)p->hidden,
+                                                            reinterpret_cast<__nv_bfloat16*>(dx_rows), dx_ld);
+      break;
+    default:
+      dx_reduce_kernel<float><<<grid, 256, 0, st>>>(part, w.dx_splits, ss, (int)rows, (int)p->hidden,
+                                                    reinterpret_cast<float*>(dx_rows), dx_ld);
+  }
+  return check_launch();
+}
+
+int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0, int64_t rows, void* workspace,
+                 float* dweight_acc, int64_t dw_ld, int32_t first, void* dweight_final, int64_t dwf_ld,
+                 void* stream) {
+  int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if ((v = check_chunk(p, row0, rows)) != LCE_OK) return v;
+  if (!p->want_grad || !x || !workspace) return LCE_ERR_INVALID_ARGUMENT;
+  if (x_ld < p->hidden) return LCE_ERR_INVALID_ARGUMENT;
+  // the fp32 accumulator is needed unless this single call both starts and finishes the accumulation
+  const bool need_acc = !(first && dweight_final != nullptr);
+  if (need_acc && (!dweight_acc || dw_ld < p->vocab_local)) return LCE_ERR_INVALID_ARGUMENT;
+  if (dweight_final && dwf_ld < p->vocab_local) return LCE_ERR_INVALID_ARGUMENT;
+  if (dweight_acc && ((reinterpret_cast<uintptr_t>(dweight_acc) & 15u) != 0 || (dw_ld & 3) != 0))
+    return LCE_ERR_MISALIGNED;
+  if (dweight_final && ((reinterpret_cast<uintptr_t>(dweight_final) & 15u) != 0 || (dwf_ld & 7) != 0))
+    return LCE_ERR_MISALIGNED;
+  int sms = 0;
+  if ((v = ensure_device(&sms)) != LCE_OK) return v;
+  cudaStream_t st = (cudaStream_t)stream;
+  const Workspace w = layout_workspace(p, workspace, sms);
+  const int es = elem_size(p->dtype);
+  const long long local0 = row0 % p->chunk_rows;
+
+  // dW (+)= x^T * dZ, scaled by logit_scale / n_valid
+  const bool pair = use_pair_kernel(p->hidden / BLOCK_M, sms);
+  CUtensorMap ta, tb;
+  if ((v = make_operand_tmap(&ta, p->dtype, true, x, p->hidden, p->n_rows_total, x_ld, BLOCK_M)) != LCE_OK) return v;
+  if ((v = make_operand_tmap(&tb, p->dtype, true, w.slab, p->vocab_local, p->chunk_rows, p->vocab_local,
+                             rows_of_b_tile(pair))) != LCE_OK)
+    return v;
+  GemmParams gp;
+  memset(&gp, 0, sizeof(gp));
+  gp.m_tiles = (int)(p->hidden / BLOCK_M);
+  gp.n_tiles = (int)(p->vocab_local / BLOCK_N);
+  gp.splits = 1;
+  gp.k_blocks = (int)(rows * es / 128);
+  gp.a_k0 = (int)row0;
+  gp.b_k0 = (int)local0;
+  gp.out = dweight_acc;
+  gp.out_ld = dw_ld;
+  gp.out_split_stride = 0;
+  gp.accumulate = first ? 0 : 1;
+  gp.out_scale = p->logit_scale;
+  gp.out_div = &w.scalars->n_valid;
+  gp.out_final = dweight_final;
+  gp.out_final_ld = dwf_ld;
+  gp.status = &w.scalars->status;
   {
-    if ((v = make_operand_tmap(&ta, p->dtype, true, x, p->hidden, p->n_rows_total, x_ld, BLOCK_M)) != LCE_OK)
-      return v;
-    if ((v = make_operand_tmap(&tb, p->dtype, true, w.slab, p->vocab_local, p->chunk_rows, p->vocab_local,
-                               BLOCK_N)) != LCE_OK)
-      return v;
-    GemmParams gp;
-    memset(&gp, 0, sizeof(gp));
-    gp.m_tiles = (int)(p->hidden / BLOCK_M);
-    gp.n_tiles = n_vtiles;
-    gp.splits = 1;
-    gp.k_blocks = (int)(rows * es / 128);
-    gp.a_k0 = (int)row0;
-    gp.out = dweight;
-    gp.out_ld = dw_ld;
-    gp.out_split_stride = 0;
-    gp.accumulate = first_chunk ? 0 : 1;
-    gp.out_scale = p->logit_scale;
-    gp.out_div = &w.scalars->n_valid;
-    gp.status = &w.scalars->status;
-    {
-      ProfScope prof(PROF_DW, st);
-      v = launch_gemm_dtype<true, true, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st);
-    }
-    if (v != LCE_OK) return v;
+    ProfScope prof(PROF_DW, st);
+    v = launch_gemm_dtype<true, true, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st, pair);
   }
-  return LCE_OK;
+  return v;
+}
+
+int lce_backward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
+                       const int64_t* labels, int64_t row0, int64_t rows, void* workspace, void* dx, int64_t dx_ld,
+                       int32_t dx_dtype, float* dweight_acc, int64_t dw_ld, int32_t first, void* dweight_final,
+                       int64_t dwf_ld, void* stream) {
+  int v = lce_dz_chunk(p, labels, row0, rows, workspace, stream);
+  if (v != LCE_OK) return v;
+  if ((v = lce_dx_chunk(p, weight, w_ld, row0, rows, workspace, dx, dx_ld, dx_dtype, stream)) != LCE_OK) return v;
+  return lce_dw_chunk(p, x, x_ld, row0, rows, workspace, dweight_acc, dw_ld, first, dweight_final, dwf_ld, stream);
 }
 
 int lce_finalize(const lce_problem* p, void* workspace, float* out5, void* stream) {
@@ -548,19 +627,19 @@ int lce_finalize(const lce_problem* p, void* workspace, float* out5, void* strea
 namespace {
 template <typename S>
 int scale_cast_dst(const S* src, long long src_ld, void* dst, int dst_dtype, long long dst_ld, long long rows,
-                   long long cols, const float* f, int grid, cudaStream_t st) {
+                   long long cols, const float* f, int grid, cudaStream_t st, int skip) {
   switch (dst_dtype) {
     case LCE_DTYPE_F16:
       scale_cast_kernel<S, __half><<<grid, 256, 0, st>>>(src, src_ld, reinterpret_cast<__half*>(dst), dst_ld, rows,
-                                                         cols, f);
+                                                         cols, f, skip);
       break;
     case LCE_DTYPE_BF16:
       scale_cast_kernel<S, __nv_bfloat16><<<grid, 256, 0, st>>>(src, src_ld, reinterpret_cast<__nv_bfloat16*>(dst),
-                                                                dst_ld, rows, cols, f);
+                                                                dst_ld, rows, cols, f, skip);
       break;
     case LCE_DTYPE_F32:
       scale_cast_kernel<S, float><<<grid, 256, 0, st>>>(src, src_ld, reinterpret_cast<float*>(dst), dst_ld, rows,
-                                                        cols, f);
+                                                        cols, f, skip);
       break;
     default: return LCE_ERR_INVALID_ARGUMENT;
   }
@@ -574,19 +653,26 @@ int lce_grad_scale_cast(const void* src, int32_t src_dtype, int64_t src_ld, void
                         int64_t dst_ld, int64_t rows, int64_t cols, const float* dev_factor, void* stream) {
   if (!src || !dst || !dev_factor || rows <= 0 || cols <= 0 || src_ld < cols || dst_ld < cols)
     return LCE_ERR_INVALID_ARGUMENT;
+  if (cols % 8 != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
+  auto aligned = [](const void* ptr, long long ld, int dtype) {
+    const long long es = dtype == LCE_DTYPE_F32 ? 4 : 2;
+    return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && ((ld * es) & 15) == 0;
+  };
+  if (!aligned(src, src_ld, src_dtype) || !aligned(dst, dst_ld, dst_dtype)) return LCE_ERR_MISALIGNED;
   const int sms = sm_count_or_default();
-  const int grid = grid_for(rows * cols, 256 * 4, sms, 8);
+  const int grid = grid_for(rows * (cols / 8), 256, sms, 16);
+  const int skip = (src == dst && src_dtype == dst_dtype) ? 1 : 0;
   cudaStream_t st = (cudaStream_t)stream;
   switch (src_dtype) {
     case LCE_DTYPE_F16:
       return scale_cast_dst(reinterpret_cast<const __half*>(src), src_ld, dst, dst_dtype, dst_ld, rows, cols,
-                            dev_factor, grid, st);
+                            dev_factor, grid, st, skip);
     case LCE_DTYPE_BF16:
       return scale_cast_dst(reinterpret_cast<const __nv_bfloat16*>(src), src_ld, dst, dst_dtype, dst_ld, rows, cols,
-                            dev_factor, grid, st);
+                            dev_factor, grid, st, skip);
     case LCE_DTYPE_F32:
       return scale_cast_dst(reinterpret_cast<const float*>(src), src_ld, dst, dst_dtype, dst_ld, rows, cols,
-                            dev_factor, grid, st);
+                            dev_factor, grid, st, skip);
   }
   return LCE_ERR_INVALID_ARGUMENT;
 }
@@ -598,6 +684,12 @@ int lce_read_status(void* workspace, void* stream) {
     return LCE_ERR_CUDA;
   if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return LCE_ERR_CUDA;
   return host.status == 0 ? LCE_OK : LCE_ERR_DEVICE_TIMEOUT;
+}
+
+int lce_set_gemm_variant(int32_t variant) {
+  if (variant != 0 && variant != 1) return LCE_ERR_INVALID_ARGUMENT;
+  g_gemm_variant.store(variant, std::memory_order_relaxed);
+  return LCE_OK;
 }
 
 int lce_profile_enable(int32_t enable) {
@@ -640,12 +732,13 @@ int lce_debug_gemm(int32_t dtype, int32_t a_mn_major, int32_t b_mn_major, const 
   int sms = 0;
   int v = ensure_device(&sms);
   if (v != LCE_OK) return v;
+  const bool pair = use_pair_kernel(m / BLOCK_M, sms);
   CUtensorMap ta, tb;
   v = a_mn_major ? make_operand_tmap(&ta, dtype, true, a, m, k, a_ld, BLOCK_M)
                  : make_operand_tmap(&ta, dtype, false, a, k, m, a_ld, BLOCK_M);
   if (v != LCE_OK) return v;
-  v = b_mn_major ? make_operand_tmap(&tb, dtype, true, b, n, k, b_ld, BLOCK_N)
-                 : make_operand_tmap(&tb, dtype, false, b, k, n, b_ld, BLOCK_N);
+  v = b_mn_major ? make_operand_tmap(&tb, dtype, true, b, n, k, b_ld, rows_of_b_tile(pair))
+                 : make_operand_tmap(&tb, dtype, false, b, k, n, b_ld, rows_of_b_tile(pair));
   if (v != LCE_OK) return v;
   GemmParams gp;
   memset(&gp, 0, sizeof(gp));
@@ -658,11 +751,13 @@ int lce_debug_gemm(int32_t dtype, int32_t a_mn_major, int32_t b_mn_major, const 
   gp.out_split_stride = m * n;
   gp.out_scale = 1.f;
   gp.status = dev_status;
+  gp.clock_probe = reinterpret_cast<long long*>(dev_status + 2);
   cudaStream_t st = (cudaStream_t)stream;
-  if (!a_mn_major && !b_mn_major) return launch_gemm_dtype<false, false, EPI_F32, false>(dtype, ta, tb, gp, sms, st);
-  if (!a_mn_major && b_mn_major) return launch_gemm_dtype<false, true, EPI_F32, false>(dtype, ta, tb, gp, sms, st);
-  if (a_mn_major && !b_mn_major) return launch_gemm_dtype<true, false, EPI_F32, false>(dtype, ta, tb, gp, sms, st);
-  return launch_gemm_dtype<true, true, EPI_F32, false>(dtype, ta, tb, gp, sms, st);
+  if (!a_mn_major && !b_mn_major)
+    return launch_gemm_dtype<false, false, EPI_F32, false>(dtype, ta, tb, gp, sms, st, pair);
+  if (!a_mn_major && b_mn_major) return launch_gemm_dtype<false, true, EPI_F32, false>(dtype, ta, tb, gp, sms, st, pair);
+  if (a_mn_major && !b_mn_major) return launch_gemm_dtype<true, false, EPI_F32, false>(dtype, ta, tb, gp, sms, st, pair);
+  return launch_gemm_dtype<true, true, EPI_F32, false>(dtype, ta, tb, gp, sms, st, pair);
 }
 
 }  // extern "C"

@@ -66,26 +66,57 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Wait limit for every in-kernel wait. A healthy wait lasts microseconds; the limit only
 // exists so that a protocol error ends the kernel with an error status instead of a hang.
-constexpr uint64_t kWaitLimitNs = 4000000000ull;   // 4 s
-constexpr uint32_t kWaitLimitIters = 1u << 30;     // backstop should the timer not advance
+// Measured in SM clock cycles (clock64 is a cheap register read, unlike the global timer).
+constexpr long long kWaitLimitCycles = 8000000000ll;  // about 4 to 7 s at 1.1 - 1.9 GHz
+constexpr uint32_t kWaitLimitIters = 1u << 30;        // backstop
 
 // Bounded wait on one phase of an mbarrier. `abort_flag` is a CTA-shared word: any role that
-// gives up sets it, and the other roles notice it within a few hundred polls.
+// gives up sets it, and the other roles notice it within a thousand polls. The first polls touch
+// nothing but the barrier, so that a wait that is about to succeed costs no extra latency.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  uint32_t it = 0;
-  while (true) {
+  long long t0 = 0;
+#pragma unroll 1
+  for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    ++it;
-    if ((it & 0xFFu) == 0u) {
+    if ((it & 0x3FFu) == 0x3FFu) {
       if (*abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs || it > kWaitLimitIters) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitCycles || it > kWaitLimitIters) {
         *abort_flag = 1;
         return false;
       }
     }
   }
+}
+
+// Same bounded wait for a whole warp that expects to wait long (an epilogue warp waiting for the next
+// accumulator): lane 0 alone polls, sleeping between polls, so that the other 31 lanes do not load the
+// shared-memory pipe that feeds the tensor cores; the result is broadcast. Call with all lanes converged.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) {
+    long long t0 = 0;
+#pragma unroll 1
+    for (uint32_t it = 0;; ++it) {
+      if (mbar_try_wait(bar, parity)) break;
+      __nanosleep(it < 64 ? 32 : 256);
+      if ((it & 0x3Fu) == 0x3Fu) {
+        if (*abort_flag != 0) {
+          ok = 0;
+          break;
+        }
+        const long long now = clock64();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > kWaitLimitCycles || it > kWaitLimitIters) {
+          *abort_flag = 1;
+          ok = 0;
+          break;
+        }
+      }
+    }
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -200,6 +231,80 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
+// CTA pairs (cluster of 2): cta_group::2 forms. The pair shares one MMA: CTA rank 0 issues it,
+// both CTAs feed operands from their own shared memory and own half of the accumulator rows.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the location `smem_addr` (a CTA-local shared address) in CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+// All threads of both CTAs.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive (count 1) on an mbarrier given by its shared::cluster address (own or peer CTA).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 2-D tile load into this CTA's shared memory whose completion bytes are counted on an mbarrier
+// that may live in the peer CTA (`bar_cluster_addr` is a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tmap, uint32_t bar_cluster_addr,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_pair_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_pair_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the mbarrier at `bar_cluster_addr` (own or peer CTA) once every tcgen05 operation this
+// thread issued so far -- pair-wide MMAs included -- has completed.
+__device__ __forceinline__ void umma_pair_commit(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
 
 // ---------------------------------------------------------------------------------------------
 // small math helpers

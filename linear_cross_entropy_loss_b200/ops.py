@@ -78,14 +78,29 @@ class NativeBackend:
             "lce_combine_chunk",
         )
 
-    def backward_chunk(self, prob, x, At, y, row0, rows, workspace, dx, dA, first_chunk):
+    def dz_chunk(self, prob, y, row0, rows, workspace):
         _native.check(
-            self.lib.lce_backward_chunk(
-                ctypes.byref(prob), _ptr(x), x.stride(0), _ptr(At), At.stride(0), _ptr(y), row0, rows,
-                _ptr(workspace), _ptr(dx), dx.stride(0), _DTYPE_CODE[dx.dtype], _ptr(dA), dA.stride(0),
-                1 if first_chunk else 0, self._stream(workspace),
+            self.lib.lce_dz_chunk(ctypes.byref(prob), _ptr(y), row0, rows, _ptr(workspace), self._stream(workspace)),
+            "lce_dz_chunk",
+        )
+
+    def dx_chunk(self, prob, At, row0, rows, workspace, dx):
+        _native.check(
+            self.lib.lce_dx_chunk(
+                ctypes.byref(prob), _ptr(At), At.stride(0), row0, rows, _ptr(workspace), _ptr(dx), dx.stride(0),
+                _DTYPE_CODE[dx.dtype], self._stream(workspace),
             ),
-            "lce_backward_chunk",
+            "lce_dx_chunk",
+        )
+
+    def dw_chunk(self, prob, x, row0, rows, workspace, dW_acc, first, dW_final):
+        _native.check(
+            self.lib.lce_dw_chunk(
+                ctypes.byref(prob), _ptr(x), x.stride(0), row0, rows, _ptr(workspace), _ptr(dW_acc),
+                0 if dW_acc is None else dW_acc.stride(0), 1 if first else 0, _ptr(dW_final),
+                0 if dW_final is None else dW_final.stride(0), self._stream(workspace),
+            ),
+            "lce_dw_chunk",
         )
 
     def finalize(self, prob, workspace, out5):
@@ -139,9 +154,24 @@ class ShardSpec:
     reduce_dx: Callable[[torch.Tensor], None]
 
 
-def grad_buffer_dtype(dtype: torch.dtype) -> torch.dtype:
-    """dx is kept in fp32 for bf16 inputs and in the input type otherwise (reference ops.py:693-694)."""
-    return torch.float32 if dtype == torch.bfloat16 else dtype
+# A chunk whose row count allows it is processed as this many sub-chunks, so that the memory-bound slab transform
+# of one sub-chunk runs on a second stream underneath the tensor-core kernels of the other.
+SUBCHUNKS = 2
+_side_streams: dict = {}
+
+
+def _side_stream(device: torch.device):
+    key = (device.type, device.index)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device)
+    return _side_streams[key]
+
+
+def _split_rows(row0: int, rows: int):
+    """Sub-chunks of a chunk: halves when each half keeps the 256-row granularity of the CTA-pair kernels."""
+    if SUBCHUNKS == 2 and rows >= 1024 and rows % 512 == 0:
+        return [(row0, rows // 2), (row0 + rows // 2, rows // 2)]
+    return [(row0, rows)]
 
 
 def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size, monitoring, want_grad,
@@ -149,12 +179,16 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     """One forward(+gradient) pass over all row chunks.
 
     x: (N, H) with unit inner stride, y: (N,) int64 contiguous, At: (H, V_local) with unit inner stride.
-    Returns (out5, dx, dA, workspace): out5 = float32[5] (loss, z_value, logit_max, logit_entropy,
-    logit_norm); dx (N, H) in grad_buffer_dtype(x.dtype) and dA (H, V_local) float32, or None without
-    want_grad. Follows the chunk loop of the reference (ops.py:721-791).
+    Returns (out5, dx, dW, workspace): out5 = float32[5] (loss, z_value, logit_max, logit_entropy,
+    logit_norm); dx (N, H) and dW (H, V_local) in the dtype of x / At, or None without want_grad.
+    Follows the chunk loop of the reference (ops.py:721-791). Per chunk, on the caller's stream:
+    forward of each sub-chunk, then dx of each sub-chunk, then one dW accumulation over the whole chunk; on
+    a second stream, as soon as a sub-chunk's forward is done: [all-gather of the row partials,] log-sum-exp
+    combine and the in-place slab transform -- which therefore overlap the next tensor-core kernel.
     """
     backend = get_backend()
-    if getattr(backend, "requires_cuda", True) and not (x.is_cuda and y.is_cuda and At.is_cuda):
+    native = getattr(backend, "requires_cuda", True)
+    if native and not (x.is_cuda and y.is_cuda and At.is_cuda):
         raise RuntimeError("linear_cross_entropy_loss_b200 runs on CUDA tensors only; there is no CPU fallback")
     N, H = x.shape
     H_A, V = At.shape
@@ -178,28 +212,59 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
         logit_scale=float(logit_scale), z_regularization=float(z_regularization),
     )
     dev = x.device
+    n_chunks = -(-N // N_group)
     workspace = torch.empty(backend.workspace_bytes(prob), dtype=torch.uint8, device=dev)
     row_parts = torch.empty(ROW_PARTS * N_group, dtype=torch.float32, device=dev)
     out5 = torch.empty(5, dtype=torch.float32, device=dev)
-    dx = dA = None
+    dx = dW = dW_acc = None
     if want_grad:
-        dx = torch.empty((N, H), dtype=grad_buffer_dtype(x.dtype), device=dev)
-        dA = torch.empty((H, V), dtype=torch.float32, device=dev)
+        dx = torch.empty((N, H), dtype=x.dtype, device=dev)
+        dW = torch.empty((H, V), dtype=At.dtype, device=dev)
+        if n_chunks > 1:  # fp32 accumulator across chunks; the last chunk writes dW from it
+            dW_acc = torch.empty((H, V), dtype=torch.float32, device=dev)
+
+    main = torch.cuda.current_stream(dev) if (native and dev.type == "cuda") else None
+    side = _side_stream(dev) if main is not None else None
+
+    def on_side(after_event):
+        if side is None:
+            return contextlib.nullcontext()
+        side.wait_event(after_event)
+        return torch.cuda.stream(side)
 
     backend.begin(prob, y, workspace)
-    first = True
-    for row0 in range(0, N, N_group):
+    for ci, row0 in enumerate(range(0, N, N_group)):
         rows = min(N_group, N - row0)
-        backend.forward_chunk(prob, x, At, y, row0, rows, workspace, row_parts)
-        parts_all = row_parts if shard is None else shard.gather_row_parts(row_parts)
-        backend.combine_chunk(prob, parts_all, y, row0, rows, workspace)
+        subs = _split_rows(row0, rows)
+        ready = []
+        for r0, n in subs:
+            backend.forward_chunk(prob, x, At, y, r0, n, workspace, row_parts)
+            fwd_done = None
+            if side is not None:
+                fwd_done = torch.cuda.Event()
+                fwd_done.record(main)
+            with on_side(fwd_done):
+                parts_all = row_parts if shard is None else shard.gather_row_parts(row_parts)
+                backend.combine_chunk(prob, parts_all, y, r0, n, workspace)
+                if want_grad:
+                    backend.dz_chunk(prob, y, r0, n, workspace)
+                if side is not None:
+                    done = torch.cuda.Event()
+                    done.record(side)
+                    ready.append(done)
         if want_grad:
-            backend.backward_chunk(prob, x, At, y, row0, rows, workspace, dx, dA, first)
-            if shard is not None:
-                shard.reduce_dx(dx[row0:row0 + rows])
-        first = False
+            for i, (r0, n) in enumerate(subs):
+                if side is not None:
+                    main.wait_event(ready[i])
+                backend.dx_chunk(prob, At, r0, n, workspace, dx)
+                if shard is not None:
+                    shard.reduce_dx(dx[r0:r0 + n])
+            last = ci == n_chunks - 1
+            backend.dw_chunk(prob, x, row0, rows, workspace, dW_acc, ci == 0, dW if last else None)
+    if side is not None:
+        main.wait_stream(side)
     backend.finalize(prob, workspace, out5)
-    return out5, dx, dA, workspace
+    return out5, dx, dW, workspace
 
 
 def _device_guard(t: torch.Tensor):
@@ -220,17 +285,15 @@ def _prepare(x_in, y, At):
 
 
 def _scaled_grads(ctx, grad_output):
-    """grad * grad_output in the dtype of the corresponding input (reference ops.py:804-810)."""
+    """grad * grad_output, in place (reference ops.py:804-810). The gradients already have the dtype of their
+    inputs; when grad_output is exactly 1 -- a plain loss.backward() -- the kernels leave them untouched."""
     backend = get_backend()
-    dx, dA = ctx.lce_grads
+    dx, dW = ctx.lce_grads
     ctx.lce_grads = None
     factor = grad_output.detach().reshape(1).to(device=dx.device, dtype=torch.float32).contiguous()
-    x_dtype, a_dtype = ctx.lce_dtypes
-    gx = dx if dx.dtype == x_dtype else torch.empty(dx.shape, dtype=x_dtype, device=dx.device)
-    backend.grad_scale_cast(dx, gx, factor)
-    gA = dA if dA.dtype == a_dtype else torch.empty(dA.shape, dtype=a_dtype, device=dA.device)
-    backend.grad_scale_cast(dA, gA, factor)
-    return gx.view(ctx.lce_x_shape), gA
+    backend.grad_scale_cast(dx, dx, factor)
+    backend.grad_scale_cast(dW, dW, factor)
+    return dx.view(ctx.lce_x_shape), dW
 
 
 class LinearXentImplementation(torch.autograd.Function):
@@ -249,7 +312,6 @@ class LinearXentImplementation(torch.autograd.Function):
                 out5, dx, dA, _ = run_pass(x, y_flat, A, ignore_index, z_regularization, logit_scale, N_chunk_size,
                                            monitoring, want_grad)
             ctx.lce_grads = (dx, dA) if want_grad else None
-            ctx.lce_dtypes = (x_in.dtype, At.dtype)
             ctx.lce_x_shape = x_in.shape
             loss, z_value, logit_max, logit_ent, logit_norm = out5.unbind(0)
             ctx.mark_non_differentiable(z_value, logit_max, logit_ent, logit_norm)

@@ -75,7 +75,6 @@ class VocabShardedLinearXent(torch.autograd.Function):
                                                N_chunk_size, monitoring, want_grad, shard=spec)
                 coll.wait_all()
             ctx.lce_grads = (dx, dA) if want_grad else None
-            ctx.lce_dtypes = (x_in.dtype, At_shard.dtype)
             ctx.lce_x_shape = x_in.shape
             loss, z_value, logit_max, logit_ent, logit_norm = out5.unbind(0)
             ctx.mark_non_differentiable(z_value, logit_max, logit_ent, logit_norm)

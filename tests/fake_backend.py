@@ -32,14 +32,16 @@ class FakeBackend:
         z = oracle.logits64(x[row0:row0 + rows], At, prob.logit_scale)
         yy = y[row0:row0 + rows].numpy()
         parts = oracle.row_partials(z, yy, prob.vocab_offset, prob.ignore_index)
+        local0 = row0 % prob.chunk_rows
         rp = row_parts.view(5, prob.chunk_rows)
-        rp[:, :rows] = torch.from_numpy(parts).float()
-        st["z"] = z
+        rp[:, local0:local0 + rows] = torch.from_numpy(parts).float()
+        st.setdefault("z", {})[row0] = z
 
     def combine_chunk(self, prob, row_parts_all, y, row0, rows, workspace):
         self.calls.append("combine_chunk")
         st = self.state[workspace.data_ptr()]
-        parts = row_parts_all.view(prob.world, 5, prob.chunk_rows)[:, :, :rows].double().numpy()
+        local0 = row0 % prob.chunk_rows
+        parts = row_parts_all.view(prob.world, 5, prob.chunk_rows)[:, :, local0:local0 + rows].double().numpy()
         lse, t, ent, q, m = oracle.combine_partials(parts)
         v = (y[row0:row0 + rows] != prob.ignore_index).numpy()
         st["nll"] += float(((lse - t) * v).sum())
@@ -47,12 +49,12 @@ class FakeBackend:
         st["ent"] += float((ent * v).sum())
         st["norm"] += float(np.sqrt(q).sum())
         st["zmax"] = max(st["zmax"], float(m.max()))
-        st["lse"] = lse
+        st.setdefault("lse", {})[row0] = lse
 
-    def backward_chunk(self, prob, x, At, y, row0, rows, workspace, dx, dA, first_chunk):
-        self.calls.append("backward_chunk")
+    def dz_chunk(self, prob, y, row0, rows, workspace):
+        self.calls.append("dz_chunk")
         st = self.state[workspace.data_ptr()]
-        z, lse = st["z"], st["lse"]
+        z, lse = st["z"].pop(row0), st["lse"].pop(row0)
         yy = y[row0:row0 + rows].numpy()
         v = yy != prob.ignore_index
         p = np.exp(z - lse[:, None]) * (1.0 + 2.0 * prob.z_regularization * lse)[:, None]
@@ -60,13 +62,27 @@ class FakeBackend:
         own = v & (yl >= 0) & (yl < z.shape[1])
         p[np.nonzero(own)[0], yl[own]] -= 1.0
         p *= v[:, None]
+        st.setdefault("dz", {})[row0] = p
+
+    def dx_chunk(self, prob, At, row0, rows, workspace, dx):
+        self.calls.append("dx_chunk")
+        st = self.state[workspace.data_ptr()]
         coef = prob.logit_scale / st["n_valid"]
-        dx[row0:row0 + rows] = torch.from_numpy(p @ At.double().numpy().T * coef).to(dx.dtype)
-        g = torch.from_numpy(x[row0:row0 + rows].double().numpy().T @ p * coef).float()
-        if first_chunk:
-            dA.copy_(g)
+        dx[row0:row0 + rows] = torch.from_numpy(st["dz"][row0] @ At.double().numpy().T * coef).to(dx.dtype)
+
+    def dw_chunk(self, prob, x, row0, rows, workspace, dW_acc, first, dW_final):
+        self.calls.append("dw_chunk")
+        st = self.state[workspace.data_ptr()]
+        coef = prob.logit_scale / st["n_valid"]
+        keys = sorted(k for k in st["dz"] if row0 <= k < row0 + rows)
+        dz = np.concatenate([st["dz"].pop(k) for k in keys])
+        assert dz.shape[0] == rows
+        g = torch.from_numpy(x[row0:row0 + rows].double().numpy().T @ dz * coef).float()
+        total = g if first else dW_acc + g
+        if dW_final is not None:
+            dW_final.copy_(total.to(dW_final.dtype))
         else:
-            dA.add_(g)
+            dW_acc.copy_(total)
 
     def finalize(self, prob, workspace, out5):
         self.calls.append("finalize")

@@ -112,7 +112,9 @@ def test_peak_extra_memory_stays_below_one_fp32_chunk_of_logits():
     loss.backward()
     torch.cuda.synchronize()
     peak = torch.cuda.max_memory_allocated() - before
-    grads = x.grad.numel() * 2 + W.grad.numel() * 2                 # what the caller keeps
-    fp32_grad_buffers = cfg.N * cfg.H * 4 + cfg.H * cfg.V * 4         # the reference keeps these too (ops.py:693-694)
-    budget = cfg.N_chunk_size * cfg.V * 4
-    assert peak - fp32_grad_buffers - grads <= budget, (peak, fp32_grad_buffers, grads, budget)
+    grads = x.grad.numel() * 2 + W.grad.numel() * 2   # what the caller keeps (bf16 dx and dW)
+    fp32_accumulator = cfg.H * cfg.V * 4                # dW accumulates in fp32 across chunks, like the reference's
+    #                                                     fp32 At_grad for bf16 inputs (ops.py:693)
+    budget = cfg.N_chunk_size * cfg.V * 4               # one fp32 chunk of logits: the reference's stated peak
+    assert peak - fp32_accumulator - grads <= budget, (peak, fp32_accumulator, grads, budget)
+    assert peak <= 1.5 * budget

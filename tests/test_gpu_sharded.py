@@ -41,7 +41,9 @@ def test_emulated_shards_on_one_gpu(world):
             be.forward_chunk(probs[g], xd, slabs[g], yd, row0, chunk, ws[g], parts[g])
         for g in range(world):
             be.combine_chunk(probs[g], parts, yd, row0, chunk, ws[g])
-            be.backward_chunk(probs[g], xd, slabs[g], yd, row0, chunk, ws[g], dxs[g], dWs[g], row0 == 0)
+            be.dz_chunk(probs[g], yd, row0, chunk, ws[g])
+            be.dx_chunk(probs[g], slabs[g], row0, chunk, ws[g], dxs[g])
+            be.dw_chunk(probs[g], xd, row0, chunk, ws[g], dWs[g], row0 == 0, None)
     for g in range(world):
         be.finalize(probs[g], ws[g], outs[g])
     torch.cuda.synchronize()

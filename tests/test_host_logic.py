@@ -48,7 +48,7 @@ def test_chunk_loop_matches_oracle(fake, chunk):
     np.testing.assert_allclose(x.grad.numpy(), ref.dx, atol=1e-7)
     np.testing.assert_allclose(W.grad.numpy(), ref.dW, atol=1e-7)
     n_chunks = -(-512 // min(512, chunk))
-    assert fake.calls.count("forward_chunk") == n_chunks == fake.calls.count("backward_chunk")
+    assert fake.calls.count("dw_chunk") == n_chunks and fake.calls.count("forward_chunk") == fake.calls.count("dx_chunk") >= n_chunks
     assert fake.calls[0] == "begin" and "finalize" in fake.calls
 
 
@@ -66,7 +66,7 @@ def test_grad_output_scales_both_gradients(fake):
 def test_no_gradient_work_without_requires_grad(fake):
     x, y, W = make(seed=2)
     out = linear_cross_entropy(x, y, W, ignore_index=-1)
-    assert "backward_chunk" not in fake.calls
+    assert "dx_chunk" not in fake.calls and "dw_chunk" not in fake.calls
     assert not out[0].requires_grad
     assert abs(out[0].item() - oracle.forward_backward(x, y, W, -1, want_grad=False).loss) < 1e-5
 
