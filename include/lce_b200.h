@@ -63,9 +63,9 @@ typedef struct lce_problem {
   float z_regularization; /* weight of mean(lse^2)       (ops.py:756-761)          */
 } lce_problem;
 
-/* Number of per-row partial statistics a rank exports per chunk (max, sumexp, target logit,
- * sum exp*z, sum z^2); lce_forward_chunk writes LCE_ROW_PARTS * chunk_rows floats. */
-#define LCE_ROW_PARTS 5
+/* Number of per-row partial statistics a rank exports per chunk (base b of the sums, sum exp(z - b),
+ * target logit, sum exp(z - b) z, sum z^2, max z); lce_forward_chunk writes LCE_ROW_PARTS * chunk_rows floats. */
+#define LCE_ROW_PARTS 6
 
 /* ---- housekeeping ------------------------------------------------------------------------- */
 int lce_version(void);
@@ -107,8 +107,13 @@ int lce_combine_chunk(const lce_problem* p, const float* row_parts_all, const in
  * [row0, row0 + rows) of one chunk; a call may cover a 128-aligned part of a chunk, which is how the
  * host overlaps the slab transform of one half chunk with the tensor-core work of the other):
  *
- * lce_dz_chunk   turns the slab rows from exp(z - tile max) into dZ = softmax*(1 + 2 z_reg lse) - onehot
- *                in place (ops.py:309-314). Needs lce_combine_chunk of the same rows.
+ * lce_dz_chunk   prepares dZ = softmax*(1 + 2 z_reg lse) - onehot (ops.py:309-314) from the slab the forward
+ *                wrote. fp16: the slab holds exp(z - tile max) and is rewritten in place (one pass over it).
+ *                bf16 / fp32: the slab holds exp(z - b_i) with one base b_i per row, so dZ is the slab times a
+ *                per-row factor c_i = exp(b_i - lse_i)(1 + 2 z_reg lse_i) minus the one-hot; only the label
+ *                entry of each row is touched (slab[i, y_i] -= 1/c_i), c_i goes into the epilogue of dx and
+ *                into a scaled copy c_i * x_i of the chunk's x rows that dW is computed from.
+ *                Needs lce_combine_chunk of the same rows.
  * lce_dx_chunk   dx rows = dZ W^T * logit_scale / n_valid (ops.py:317,332). dx: [n_rows_total, hidden]
  *                with row stride dx_ld and element type dx_dtype (LCE_DTYPE_*).
  * lce_dw_chunk   dW (+)= x^T dZ * logit_scale / n_valid (ops.py:424,443) accumulated in fp32:
@@ -118,8 +123,8 @@ int lce_combine_chunk(const lce_problem* p, const float* row_parts_all, const in
  *                dwf_ld) and dweight_acc is only read. A pass of a single call (first != 0 and dweight_final
  *                given) needs no dweight_acc at all (may be null).
  * lce_backward_chunk = the three in sequence. */
-int lce_dz_chunk(const lce_problem* p, const int64_t* labels, int64_t row0, int64_t rows, void* workspace,
-                 void* stream);
+int lce_dz_chunk(const lce_problem* p, const void* x, int64_t x_ld, const int64_t* labels, int64_t row0,
+                 int64_t rows, void* workspace, void* stream);
 int lce_dx_chunk(const lce_problem* p, const void* weight, int64_t w_ld, int64_t row0, int64_t rows, void* workspace,
                  void* dx, int64_t dx_ld, int32_t dx_dtype, void* stream);
 int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0, int64_t rows, void* workspace,

@@ -19,7 +19,7 @@ LIB_PATH = _PKG_DIR / "liblce_b200.so"
 
 LCE_OK = 0
 DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
-ROW_PARTS = 5
+ROW_PARTS = 6
 
 _lock = threading.Lock()
 _lib = None
@@ -104,7 +104,7 @@ SIGNATURES = {
     "lce_begin": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _vp, _vp]),
     "lce_forward_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _vp, _vp]),
     "lce_combine_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _vp, _i64, _i64, _vp, _vp]),
-    "lce_dz_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _i64, _vp, _vp]),
+    "lce_dz_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _i64, _vp, _vp]),
     "lce_dx_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _vp]),
     "lce_dw_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _vp, _i64, _vp]),
     "lce_backward_chunk": (

@@ -24,10 +24,15 @@ struct PassScalars {
   float max_logit;   // max over ALL rows and columns of z
   float n_valid;     // number of rows whose label is not ignore_index
   int status;        // device status word, 0 = ok
-  int pad;
+  int rescue;        // row-reference mode: set when a row's max logit is more than kRefRange from its reference
 };
 
-constexpr int ROW_PARTS = 5;  // max, sumexp, target logit, sum exp*z, sum z^2
+// Per-row partials a rank exports per chunk:
+//   [0] base b (the reference the sums are relative to), [1] sum_j exp(z - b), [2] target logit (0 if not owned),
+//   [3] sum_j exp(z - b) z, [4] sum_j z^2, [5] max_j z
+constexpr int ROW_PARTS = 6;
+// |row max - reference| beyond which the forward of a chunk is re-run with reference = row max
+constexpr float kRefRange = 60.f;
 
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ double block_sum_double(double v, double* scratch /*[32]*/) {
@@ -72,7 +77,7 @@ __global__ void begin_kernel(const long long* __restrict__ labels, long long n, 
     sc->max_logit = -INFINITY;
     sc->n_valid = (float)total;
     sc->status = 0;
-    sc->pad = 0;
+    sc->rescue = 0;
   }
 }
 
@@ -131,6 +136,63 @@ row_stats_kernel(const float* __restrict__ tile_max, const float* __restrict__ t
     parts[2 * stat_ld + r] = own ? target_logit[r] : 0.f;
     parts[3 * stat_ld + r] = u;
     parts[4 * stat_ld + r] = q;
+    parts[5 * stat_ld + r] = m;
+  }
+}
+
+// Row-reference mode: all tiles of a row share the reference ref_i (0, or row_ref[i] in a re-run), so the
+// per-tile sums add up. Same thread layout as row_stats_kernel. Also writes row_ref_out[i] = row max (the
+// reference a re-run would use), row_base_out[i] = ref_i, and raises *rescue when |row max - ref_i| > kRefRange.
+// run_if: when non-null and 0 the kernel does nothing (it belongs to a conditional re-run).
+template <bool kMonitor>
+__global__ void __launch_bounds__(256)
+row_stats_rowref_kernel(const float* __restrict__ tile_max, const float* __restrict__ tile_sum,
+                        const float* __restrict__ tile_ez, const float* __restrict__ tile_sq,
+                        const float* __restrict__ target_logit, const long long* __restrict__ labels, int rows,
+                        int n_tiles, long long stat_ld, long long ignore_index, long long vocab_offset,
+                        long long vocab_local, const float* row_ref_in, float* row_ref_out, float* row_base_out,
+                        int* rescue, const int* run_if, float* __restrict__ parts) {
+  if (run_if != nullptr && *run_if == 0) return;
+  __shared__ float sm[8][4][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 32 + lane;
+  float m = -INFINITY, s = 0.f, u = 0.f, q = 0.f;
+  if (r < rows) {
+    for (int t = warp; t < n_tiles; t += 8) {
+      const long long i = (long long)t * stat_ld + r;
+      m = fmaxf(m, tile_max[i]);
+      s += tile_sum[i];
+      if (kMonitor) {
+        u += tile_ez[i];
+        q += tile_sq[i];
+      }
+    }
+  }
+  sm[warp][0][lane] = m;
+  sm[warp][1][lane] = s;
+  sm[warp][2][lane] = u;
+  sm[warp][3][lane] = q;
+  __syncthreads();
+  if (warp == 0 && r < rows) {
+    for (int w = 1; w < 8; ++w) {
+      m = fmaxf(m, sm[w][0][lane]);
+      s += sm[w][1][lane];
+      u += sm[w][2][lane];
+      q += sm[w][3][lane];
+    }
+    const float ref = (row_ref_in != nullptr) ? row_ref_in[r] : 0.f;
+    const long long yv = labels[r];
+    const long long yl = yv - vocab_offset;
+    const bool own = (yv != ignore_index) && yl >= 0 && yl < vocab_local;
+    parts[0 * stat_ld + r] = ref;
+    parts[1 * stat_ld + r] = s;
+    parts[2 * stat_ld + r] = own ? target_logit[r] : 0.f;
+    parts[3 * stat_ld + r] = u;
+    parts[4 * stat_ld + r] = q;
+    parts[5 * stat_ld + r] = m;
+    row_base_out[r] = ref;
+    row_ref_out[r] = m;
+    if (!(fabsf(m - ref) <= kRefRange)) *rescue = 1;  // also catches NaN / inf
   }
 }
 
@@ -144,12 +206,13 @@ combine_kernel(const float* __restrict__ parts_all, int world, const long long* 
   double a_nll = 0.0, a_lse2 = 0.0, a_ent = 0.0, a_norm = 0.0;
   float a_max = -INFINITY;
   for (int r = threadIdx.x; r < rows; r += blockDim.x) {
-    float m = -INFINITY, s = 0.f, u = 0.f, t = 0.f, q = 0.f;
+    float m = -INFINITY, s = 0.f, u = 0.f, t = 0.f, q = 0.f, zmax = -INFINITY;
     for (int g = 0; g < world; ++g) {
       const float* pg = parts_all + (long long)g * ROW_PARTS * stat_ld;
       lse_merge(m, s, u, pg[0 * stat_ld + r], pg[1 * stat_ld + r], pg[3 * stat_ld + r]);
       t += pg[2 * stat_ld + r];
       q += pg[4 * stat_ld + r];
+      zmax = fmaxf(zmax, pg[5 * stat_ld + r]);
     }
     const float lse = m + logf(s);
     lse_out[r] = lse;
@@ -161,7 +224,7 @@ combine_kernel(const float* __restrict__ parts_all, int world, const long long* 
     }
     if (monitoring) {
       a_norm += sqrt((double)q);
-      a_max = fmaxf(a_max, m);
+      a_max = fmaxf(a_max, zmax);
     }
   }
   const double t_nll = block_sum_double(a_nll, scratch_d);
@@ -175,6 +238,7 @@ combine_kernel(const float* __restrict__ parts_all, int world, const long long* 
     sc->sum_ent += t_ent;
     sc->sum_norm += t_norm;
     sc->max_logit = fmaxf(sc->max_logit, t_max);
+    sc->rescue = 0;  // the chunk's conditional re-run (if any) is behind us
   }
 }
 
@@ -314,6 +378,45 @@ template <>
 __device__ __forceinline__ float cast_to_float<__half>(__half v) { return __half2float(v); }
 template <>
 __device__ __forceinline__ float cast_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// Row-reference mode, after the log-sum-exp is known. One block per row:
+//   C_i = valid_i * exp(ref_i - lse_i) * (1 + 2 z_reg lse_i)        -> row_coef[i]   (factor of dx)
+//   xs[i, :] = C_i * x[i, :]                                        (A operand of dW = xs^T slab)
+//   slab[i, y_i] -= 1 / C_i   if this rank owns column y_i          (so that C_i * slab[i, :] = dZ[i, :])
+// ref_i is the base the row's partials were computed with (parts[0]).
+template <typename T>
+__global__ void __launch_bounds__(256)
+row_finish_kernel(const T* __restrict__ x, long long x_ld, T* __restrict__ xs, long long xs_ld, int hidden,
+                  T* __restrict__ slab, long long slab_ld, const float* __restrict__ ref, const float* __restrict__ lse,
+                  const long long* __restrict__ labels, long long ignore_index, long long vocab_offset,
+                  long long vocab_local, float z_regularization, float* __restrict__ row_coef) {
+  const int r = blockIdx.x;
+  const long long yv = labels[r];
+  const bool valid = (yv != ignore_index);
+  const float l = lse[r];
+  float C = valid ? __expf(ref[r] - l) * (1.f + 2.f * z_regularization * l) : 0.f;
+  if (valid && fabsf(C) < 1e-30f) C = (C < 0.f) ? -1e-30f : 1e-30f;  // keeps 1 / C finite
+  if (threadIdx.x == 0) {
+    row_coef[r] = C;
+    const long long yl = yv - vocab_offset;
+    if (valid && yl >= 0 && yl < vocab_local) {
+      T* e = slab + (long long)r * slab_ld + yl;
+      *e = cast_from_float<T>(cast_to_float<T>(*e) - 1.f / C);
+    }
+  }
+  const T* src = x + (long long)r * x_ld;
+  T* dst = xs + (long long)r * xs_ld;
+  for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+    Vec8<T> v;
+    v.load(src + c);
+    float f[8];
+    v.to_float(f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] *= C;
+    v.from_float(f);
+    v.store(dst + c);
+  }
+}
 
 // dx[r, h] = sum_s part[s][r][h]  (fixed order s = 0, 1, ...), cast to T. cols % 4 == 0.
 template <typename T>

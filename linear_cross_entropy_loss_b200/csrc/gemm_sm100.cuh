@@ -91,6 +91,13 @@ struct GemmParams {
   long long ignore_index;
   long long vocab_offset;      // global class id of local column 0
   float scale;                 // logit scale (> 0)
+  const float* row_ref;        // [rows] row-reference mode: slab = exp(z - row_ref[i]); null = reference 0
+
+  // ---- EPI_F32: optional per-output-row factor (dx in row-reference mode: exp(ref - lse) (1 + 2 z_reg lse))
+  const float* row_coef;
+
+  // ---- all kernels: when non-null and *run_if == 0 the kernel returns at once (conditional re-run)
+  const int* run_if;
 
   int* status;                 // device status word (0 = ok)
   long long* clock_probe;      // optional [2]: SM cycles and nanoseconds CTA 0 spent in the kernel (diagnostics)
@@ -181,8 +188,10 @@ __device__ __forceinline__ void store_slab_chunk(float* dst, const float (&e)[32
 //   tile_max = max_j z,  tile_sum = sum_j exp(z - tile_max),  slab[i, j] = exp(z - tile_max)
 //   target_logit[i] = z[i, y_i] if column y_i lies in this tile
 //   monitoring: tile_ez = sum_j exp(z - tile_max) * z,  tile_sq = sum_j z^2
+// Two passes over the accumulator (max first). Used for fp16, whose narrow exponent range needs the
+// exponentials normalised per tile; the slab is rescaled to the row's log-sum-exp afterwards.
 template <int kKind, bool kMonitor>
-__device__ __forceinline__ void epilogue_forward(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk,
+__device__ __forceinline__ void epilogue_forward_tilemax(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk,
                                                  int row_in_tile) {
   using Elem = typename SlabElem<kKind>::type;
   const long long r = (long long)m_blk * BLOCK_M + row_in_tile;
@@ -240,6 +249,78 @@ __device__ __forceinline__ void epilogue_forward(const GemmParams& p, uint32_t t
   if (ycol >= 0) p.target_logit[r] = tv * p.scale;
 }
 
+// Forward epilogue, row-reference mode (bf16 and fp32 slabs, whose exponent range is that of fp32): one pass.
+//   slab[i, j] = exp(z - ref_i),  tile_sum = sum_j exp(z - ref_i),  tile_max = max_j z
+//   monitoring: tile_ez = sum_j exp(z - ref_i) * z,  tile_sq = sum_j z^2
+// ref_i is the same for every tile of row i (0 unless the pass is a re-run with ref_i = row max), so the tile
+// sums of a row simply add up and dZ = exp(ref_i - lse_i) (1 + 2 z_reg lse_i) * slab - onehot needs only a
+// PER-ROW factor: the slab feeds the gradient GEMMs as it is. If |row max - ref_i| turns out to exceed 60 the
+// host-side sequence re-runs the chunk with ref_i = row max (see row_stats_rowref_kernel).
+template <int kKind, bool kMonitor>
+__device__ __forceinline__ void epilogue_forward_rowref(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk,
+                                                        int row_in_tile) {
+  using Elem = typename SlabElem<kKind>::type;
+  const long long r = (long long)m_blk * BLOCK_M + row_in_tile;
+  const long long yv = p.labels[r];
+  const long long ycol_ll = yv - p.vocab_offset - (long long)n_blk * BLOCK_N;
+  const int ycol = (yv != p.ignore_index && ycol_ll >= 0 && ycol_ll < BLOCK_N) ? (int)ycol_ll : -1;
+  const float ref = (p.row_ref != nullptr) ? p.row_ref[r] : 0.f;
+  const float sl2 = p.scale * 1.4426950408889634f;  // scale * log2(e)
+  const float neg_ref = -ref * 1.4426950408889634f;
+
+  float mx = -INFINITY, s = 0.f, ez = 0.f, sq = 0.f, tv = 0.f;
+  Elem* slab_row = reinterpret_cast<Elem*>(p.slab) + r * p.slab_ld + (long long)n_blk * BLOCK_N;
+#pragma unroll 1
+  for (int c = 0; c < BLOCK_N / 32; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + c * 32, v);
+    tmem_ld_wait();
+    float e[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float f = __uint_as_float(v[i]);
+      mx = fmaxf(mx, f);
+      e[i] = fast_exp2(fmaf(f, sl2, neg_ref));
+      s += e[i];
+      if (kMonitor) {
+        ez = fmaf(e[i], f, ez);
+        sq = fmaf(f, f, sq);
+      }
+    }
+    if ((ycol >> 5) == c) {
+      const int sel = ycol & 31;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i == sel) tv = __uint_as_float(v[i]);
+    }
+    if (p.store_slab) store_slab_chunk(slab_row + c * 32, e);
+  }
+
+  const long long si = (long long)n_blk * p.stat_ld + r;
+  p.tile_max[si] = mx * p.scale;
+  p.tile_sum[si] = s;
+  if (kMonitor) {
+    p.tile_ez[si] = ez * p.scale;
+    p.tile_sq[si] = sq * p.scale * p.scale;
+  }
+  if (ycol >= 0) p.target_logit[r] = tv * p.scale;
+}
+
+// fp16 slabs are normalised per tile, bf16 / fp32 slabs per row.
+template <int kKind>
+struct ForwardMode {
+  static constexpr bool kRowRef = (kKind != KIND_F16);
+};
+
+template <int kKind, bool kMonitor>
+__device__ __forceinline__ void epilogue_forward(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk,
+                                                 int row_in_tile) {
+  if (ForwardMode<kKind>::kRowRef)
+    epilogue_forward_rowref<kKind, kMonitor>(p, taddr, m_blk, n_blk, row_in_tile);
+  else
+    epilogue_forward_tilemax<kKind, kMonitor>(p, taddr, m_blk, n_blk, row_in_tile);
+}
+
 // Plain fp32 epilogue: result = coef * acc (+ out[split][row, col] when accumulating); the result is stored
 // to out, or -- converted to the input element type -- to out_final when that is given.
 template <int kKind>
@@ -249,7 +330,8 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr
   const long long row = (long long)m_blk * BLOCK_M + row_in_tile;
   float* dst = p.out + (long long)split * p.out_split_stride + row * p.out_ld + (long long)n_blk * BLOCK_N;
   Elem* dst_final = reinterpret_cast<Elem*>(p.out_final) + row * p.out_final_ld + (long long)n_blk * BLOCK_N;
-  const float coef = (p.out_div != nullptr) ? p.out_scale / __ldg(p.out_div) : p.out_scale;
+  float coef = (p.out_div != nullptr) ? p.out_scale / __ldg(p.out_div) : p.out_scale;
+  if (p.row_coef != nullptr) coef *= p.row_coef[row];
 #pragma unroll 1
   for (int c = 0; c < BLOCK_N / 32; ++c) {
     uint32_t v[32];
@@ -298,6 +380,7 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   GemmShared* sh = reinterpret_cast<GemmShared*>(tiles + size_t(kStages) * kStageBytes);
   volatile int* abort_flag = &sh->abort_flag;
+  if (p.run_if != nullptr && *p.run_if == 0) return;  // uniform over the grid: nothing has been set up yet
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -488,10 +571,7 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // MMA batch to empty[stage] of BOTH CTAs and each finished accumulator to acc_full of both; the epilogue
 // warps of both CTAs arrive on CTA 0's acc_empty (8 arrivals).
 // --------------------------------------------------------------------------------------------------
-#ifndef LCE_PAIR_STAGES
-#define LCE_PAIR_STAGES 6
-#endif
-constexpr int kPairStages = LCE_PAIR_STAGES;
+constexpr int kPairStages = 6;
 constexpr int kPairBTileBytes = (BLOCK_N / 2) * 128;  // 16 KiB: this CTA's half of the B tile
 constexpr int kPairStageBytes = kATileBytes + kPairBTileBytes;
 constexpr int PAIR_M = 2 * BLOCK_M;
@@ -533,6 +613,7 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   GemmPairShared* sh = reinterpret_cast<GemmPairShared*>(tiles + size_t(kPairStages) * kPairStageBytes);
   volatile int* abort_flag = &sh->abort_flag;
+  if (p.run_if != nullptr && *p.run_if == 0) return;  // uniform over the grid: nothing has been set up yet
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;

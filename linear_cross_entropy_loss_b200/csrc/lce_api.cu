@@ -143,11 +143,19 @@ struct Workspace {
   float* tile_sq;
   float* target_logit;
   float* lse;
+  float* row_ref;   // row-reference mode: row max of the first forward = reference of a conditional re-run
+  float* row_base;  // row-reference mode: the reference the row's slab and sums were computed with
+  float* row_coef;  // row-reference mode: exp(base - lse) (1 + 2 z_reg lse), 0 for ignored rows
   void* slab;
+  void* xs;         // row-reference mode: row_coef[i] * x[i, :] for the rows of the chunk
   float* dx_part;
   int dx_splits;
   size_t total;
 };
+
+// fp16 slabs hold exp(z - tile max) and are rescaled in a separate pass; bf16 / fp32 slabs hold
+// exp(z - row reference) and feed the gradient GEMMs directly (see gemm_sm100.cuh).
+inline bool row_reference_mode(const lce_problem* p) { return p->dtype != LCE_DTYPE_F16; }
 
 Workspace layout_workspace(const lce_problem* p, void* base, int sms) {
   Workspace w;
@@ -168,12 +176,17 @@ Workspace layout_workspace(const lce_problem* p, void* base, int sms) {
   w.tile_sq = reinterpret_cast<float*>(take(p->monitoring ? stat_bytes : 0));
   w.target_logit = reinterpret_cast<float*>(take(rows * sizeof(float)));
   w.lse = reinterpret_cast<float*>(take(rows * sizeof(float)));
+  w.row_ref = reinterpret_cast<float*>(take(rows * sizeof(float)));
+  w.row_base = reinterpret_cast<float*>(take(rows * sizeof(float)));
+  w.row_coef = reinterpret_cast<float*>(take(rows * sizeof(float)));
   w.dx_splits = choose_dx_splits(p, sms);
   if (p->want_grad) {
     w.slab = take(rows * (size_t)p->vocab_local * elem_size(p->dtype));
+    w.xs = row_reference_mode(p) ? take(rows * (size_t)p->hidden * elem_size(p->dtype)) : nullptr;
     w.dx_part = reinterpret_cast<float*>(take((size_t)w.dx_splits * rows * (size_t)p->hidden * sizeof(float)));
   } else {
     w.slab = nullptr;
+    w.xs = nullptr;
     w.dx_part = nullptr;
   }
   w.total = off;
@@ -405,24 +418,51 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
   gp.scale = p->logit_scale;
   gp.status = &w.scalars->status;
 
-  {
-    ProfScope prof(PROF_FWD, st);
-    v = p->monitoring ? launch_gemm_dtype<false, true, EPI_FWD, true>(p->dtype, ta, tb, gp, sms, st, pair)
-                      : launch_gemm_dtype<false, true, EPI_FWD, false>(p->dtype, ta, tb, gp, sms, st, pair);
-  }
-  if (v != LCE_OK) return v;
-
   const int blocks = (int)((rows + 31) / 32);
   const long long* lab = reinterpret_cast<const long long*>(labels) + row0;
-  if (p->monitoring)
-    row_stats_kernel<true><<<blocks, 256, 0, st>>>(gp.tile_max, gp.tile_sum, gp.tile_ez, gp.tile_sq, gp.target_logit,
-                                                   lab, (int)rows, gp.n_tiles, p->chunk_rows, p->ignore_index,
-                                                   p->vocab_offset, p->vocab_local, row_parts_local + local0);
-  else
-    row_stats_kernel<false><<<blocks, 256, 0, st>>>(gp.tile_max, gp.tile_sum, gp.tile_ez, gp.tile_sq, gp.target_logit,
-                                                    lab, (int)rows, gp.n_tiles, p->chunk_rows, p->ignore_index,
-                                                    p->vocab_offset, p->vocab_local, row_parts_local + local0);
-  return check_launch();
+  float* parts = row_parts_local + local0;
+  auto run_forward = [&]() {
+    ProfScope prof(PROF_FWD, st);
+    return p->monitoring ? launch_gemm_dtype<false, true, EPI_FWD, true>(p->dtype, ta, tb, gp, sms, st, pair)
+                         : launch_gemm_dtype<false, true, EPI_FWD, false>(p->dtype, ta, tb, gp, sms, st, pair);
+  };
+
+  if (!row_reference_mode(p)) {
+    if ((v = run_forward()) != LCE_OK) return v;
+    if (p->monitoring)
+      row_stats_kernel<true><<<blocks, 256, 0, st>>>(gp.tile_max, gp.tile_sum, gp.tile_ez, gp.tile_sq,
+                                                     gp.target_logit, lab, (int)rows, gp.n_tiles, p->chunk_rows,
+                                                     p->ignore_index, p->vocab_offset, p->vocab_local, parts);
+    else
+      row_stats_kernel<false><<<blocks, 256, 0, st>>>(gp.tile_max, gp.tile_sum, gp.tile_ez, gp.tile_sq,
+                                                      gp.target_logit, lab, (int)rows, gp.n_tiles, p->chunk_rows,
+                                                      p->ignore_index, p->vocab_offset, p->vocab_local, parts);
+    return check_launch();
+  }
+
+  // Row-reference mode: forward with reference 0, then -- only if some row's max logit lies outside
+  // +-60 of it, which the statistics kernel reports through the device flag `rescue` -- the same two
+  // kernels again with reference = row max. The second pair returns at once when the flag is clear.
+  int* rescue = &w.scalars->rescue;
+  for (int pass = 0; pass < 2; ++pass) {
+    const int* run_if = pass == 0 ? nullptr : rescue;
+    const float* ref_in = pass == 0 ? nullptr : w.row_ref + local0;
+    gp.row_ref = ref_in;
+    gp.run_if = run_if;
+    if ((v = run_forward()) != LCE_OK) return v;
+    if (p->monitoring)
+      row_stats_rowref_kernel<true><<<blocks, 256, 0, st>>>(
+          gp.tile_max, gp.tile_sum, gp.tile_ez, gp.tile_sq, gp.target_logit, lab, (int)rows, gp.n_tiles,
+          p->chunk_rows, p->ignore_index, p->vocab_offset, p->vocab_local, ref_in, w.row_ref + local0,
+          w.row_base + local0, rescue, run_if, parts);
+    else
+      row_stats_rowref_kernel<false><<<blocks, 256, 0, st>>>(
+          gp.tile_max, gp.tile_sum, gp.tile_ez, gp.tile_sq, gp.target_logit, lab, (int)rows, gp.n_tiles,
+          p->chunk_rows, p->ignore_index, p->vocab_offset, p->vocab_local, ref_in, w.row_ref + local0,
+          w.row_base + local0, rescue, run_if, parts);
+    if ((v = check_launch()) != LCE_OK) return v;
+  }
+  return LCE_OK;
 }
 
 int lce_combine_chunk(const lce_problem* p, const float* row_parts_all, const int64_t* labels, int64_t row0,
@@ -442,12 +482,12 @@ int lce_combine_chunk(const lce_problem* p, const float* row_parts_all, const in
   return check_launch();
 }
 
-int lce_dz_chunk(const lce_problem* p, const int64_t* labels, int64_t row0, int64_t rows, void* workspace,
-                 void* stream) {
+int lce_dz_chunk(const lce_problem* p, const void* x, int64_t x_ld, const int64_t* labels, int64_t row0,
+                 int64_t rows, void* workspace, void* stream) {
   int v = validate_problem(p);
   if (v != LCE_OK) return v;
   if ((v = check_chunk(p, row0, rows)) != LCE_OK) return v;
-  if (!p->want_grad || !labels || !workspace) return LCE_ERR_INVALID_ARGUMENT;
+  if (!p->want_grad || !x || !labels || !workspace || x_ld < p->hidden) return LCE_ERR_INVALID_ARGUMENT;
   int sms = 0;
   if ((v = ensure_device(&sms)) != LCE_OK) return v;
   cudaStream_t st = (cudaStream_t)stream;
@@ -457,6 +497,22 @@ int lce_dz_chunk(const lce_problem* p, const int64_t* labels, int64_t row0, int6
   const long long local0 = row0 % p->chunk_rows;
   const long long* lab = reinterpret_cast<const long long*>(labels) + row0;
   char* slab = reinterpret_cast<char*>(w.slab) + (size_t)local0 * (size_t)p->vocab_local * es;
+  if (row_reference_mode(p)) {
+    // per-row factor, scaled copy of the x rows, label entry of the slab: see row_finish_kernel
+    const char* xrows = reinterpret_cast<const char*>(x) + (size_t)row0 * (size_t)x_ld * es;
+    char* xs = reinterpret_cast<char*>(w.xs) + (size_t)local0 * (size_t)p->hidden * es;
+    if (p->dtype == LCE_DTYPE_BF16)
+      row_finish_kernel<__nv_bfloat16><<<(int)rows, 256, 0, st>>>(
+          reinterpret_cast<const __nv_bfloat16*>(xrows), x_ld, reinterpret_cast<__nv_bfloat16*>(xs), p->hidden,
+          (int)p->hidden, reinterpret_cast<__nv_bfloat16*>(slab), p->vocab_local, w.row_base + local0, w.lse + local0,
+          lab, p->ignore_index, p->vocab_offset, p->vocab_local, p->z_regularization, w.row_coef + local0);
+    else
+      row_finish_kernel<float><<<(int)rows, 256, 0, st>>>(
+          reinterpret_cast<const float*>(xrows), x_ld, reinterpret_cast<float*>(xs), p->hidden, (int)p->hidden,
+          reinterpret_cast<float*>(slab), p->vocab_local, w.row_base + local0, w.lse + local0, lab, p->ignore_index,
+          p->vocab_offset, p->vocab_local, p->z_regularization, w.row_coef + local0);
+    return check_launch();
+  }
   const long long items = (rows / 8) * n_vtiles;
   const int grid = grid_for(items, 1, sms, 16);
   switch (p->dtype) {
@@ -519,6 +575,7 @@ int lce_dx_chunk(const lce_problem* p, const void* weight, int64_t w_ld, int64_t
   gp.accumulate = 0;
   gp.out_scale = p->logit_scale;
   gp.out_div = &w.scalars->n_valid;
+  gp.row_coef = row_reference_mode(p) ? w.row_coef + local0 : nullptr;
   gp.status = &w.scalars->status;
   {
     ProfScope prof(PROF_DX, st);
@@ -572,8 +629,12 @@ int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0
 
   // dW (+)= x^T * dZ, scaled by logit_scale / n_valid
   const bool pair = use_pair_kernel(p->hidden / BLOCK_M, sms);
+  const bool rowref = row_reference_mode(p);
   CUtensorMap ta, tb;
-  if ((v = make_operand_tmap(&ta, p->dtype, true, x, p->hidden, p->n_rows_total, x_ld, BLOCK_M)) != LCE_OK) return v;
+  // A operand (M = hidden, K = rows): the x rows themselves, or in row-reference mode their scaled copy
+  v = rowref ? make_operand_tmap(&ta, p->dtype, true, w.xs, p->hidden, p->chunk_rows, p->hidden, BLOCK_M)
+             : make_operand_tmap(&ta, p->dtype, true, x, p->hidden, p->n_rows_total, x_ld, BLOCK_M);
+  if (v != LCE_OK) return v;
   if ((v = make_operand_tmap(&tb, p->dtype, true, w.slab, p->vocab_local, p->chunk_rows, p->vocab_local,
                              rows_of_b_tile(pair))) != LCE_OK)
     return v;
@@ -583,7 +644,7 @@ int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0
   gp.n_tiles = (int)(p->vocab_local / BLOCK_N);
   gp.splits = 1;
   gp.k_blocks = (int)(rows * es / 128);
-  gp.a_k0 = (int)row0;
+  gp.a_k0 = (int)(rowref ? local0 : row0);
   gp.b_k0 = (int)local0;
   gp.out = dweight_acc;
   gp.out_ld = dw_ld;
@@ -605,7 +666,7 @@ int lce_backward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const 
                        const int64_t* labels, int64_t row0, int64_t rows, void* workspace, void* dx, int64_t dx_ld,
                        int32_t dx_dtype, float* dweight_acc, int64_t dw_ld, int32_t first, void* dweight_final,
                        int64_t dwf_ld, void* stream) {
-  int v = lce_dz_chunk(p, labels, row0, rows, workspace, stream);
+  int v = lce_dz_chunk(p, x, x_ld, labels, row0, rows, workspace, stream);
   if (v != LCE_OK) return v;
   if ((v = lce_dx_chunk(p, weight, w_ld, row0, rows, workspace, dx, dx_ld, dx_dtype, stream)) != LCE_OK) return v;
   return lce_dw_chunk(p, x, x_ld, row0, rows, workspace, dweight_acc, dw_ld, first, dweight_final, dwf_ld, stream);

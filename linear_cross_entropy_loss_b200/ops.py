@@ -78,9 +78,10 @@ class NativeBackend:
             "lce_combine_chunk",
         )
 
-    def dz_chunk(self, prob, y, row0, rows, workspace):
+    def dz_chunk(self, prob, x, y, row0, rows, workspace):
         _native.check(
-            self.lib.lce_dz_chunk(ctypes.byref(prob), _ptr(y), row0, rows, _ptr(workspace), self._stream(workspace)),
+            self.lib.lce_dz_chunk(ctypes.byref(prob), _ptr(x), x.stride(0), _ptr(y), row0, rows, _ptr(workspace),
+                                  self._stream(workspace)),
             "lce_dz_chunk",
         )
 
@@ -167,9 +168,10 @@ def _side_stream(device: torch.device):
     return _side_streams[key]
 
 
-def _split_rows(row0: int, rows: int):
-    """Sub-chunks of a chunk: halves when each half keeps the 256-row granularity of the CTA-pair kernels."""
-    if SUBCHUNKS == 2 and rows >= 1024 and rows % 512 == 0:
+def _split_rows(row0: int, rows: int, dtype: torch.dtype):
+    """Sub-chunks of a chunk: halves when each half keeps the 256-row granularity of the CTA-pair kernels.
+    Only fp16 has a slab-wide transform worth hiding; bf16 / fp32 run a chunk as one piece."""
+    if dtype == torch.float16 and SUBCHUNKS == 2 and rows >= 1024 and rows % 512 == 0:
         return [(row0, rows // 2), (row0 + rows // 2, rows // 2)]
     return [(row0, rows)]
 
@@ -181,10 +183,10 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     x: (N, H) with unit inner stride, y: (N,) int64 contiguous, At: (H, V_local) with unit inner stride.
     Returns (out5, dx, dW, workspace): out5 = float32[5] (loss, z_value, logit_max, logit_entropy,
     logit_norm); dx (N, H) and dW (H, V_local) in the dtype of x / At, or None without want_grad.
-    Follows the chunk loop of the reference (ops.py:721-791). Per chunk, on the caller's stream:
-    forward of each sub-chunk, then dx of each sub-chunk, then one dW accumulation over the whole chunk; on
-    a second stream, as soon as a sub-chunk's forward is done: [all-gather of the row partials,] log-sum-exp
-    combine and the in-place slab transform -- which therefore overlap the next tensor-core kernel.
+    Follows the chunk loop of the reference (ops.py:721-791): per chunk forward, [all-gather of the row
+    partials,] log-sum-exp combine, dZ preparation, dx, dW accumulation. For fp16 -- whose dZ preparation is a
+    pass over the whole slab -- a chunk runs as two sub-chunks and the combine + slab pass of one sub-chunk go
+    to a second stream, underneath the tensor-core kernels of the other.
     """
     backend = get_backend()
     native = getattr(backend, "requires_cuda", True)
@@ -223,8 +225,10 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
         if n_chunks > 1:  # fp32 accumulator across chunks; the last chunk writes dW from it
             dW_acc = torch.empty((H, V), dtype=torch.float32, device=dev)
 
-    main = torch.cuda.current_stream(dev) if (native and dev.type == "cuda") else None
-    side = _side_stream(dev) if main is not None else None
+    # second stream only where sub-chunks exist (fp16); everything else runs in order on the caller's stream
+    use_side = native and dev.type == "cuda" and x.dtype == torch.float16 and SUBCHUNKS == 2
+    main = torch.cuda.current_stream(dev) if use_side else None
+    side = _side_stream(dev) if use_side else None
 
     def on_side(after_event):
         if side is None:
@@ -235,7 +239,7 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     backend.begin(prob, y, workspace)
     for ci, row0 in enumerate(range(0, N, N_group)):
         rows = min(N_group, N - row0)
-        subs = _split_rows(row0, rows)
+        subs = _split_rows(row0, rows, x.dtype)
         ready = []
         for r0, n in subs:
             backend.forward_chunk(prob, x, At, y, r0, n, workspace, row_parts)
@@ -247,7 +251,7 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
                 parts_all = row_parts if shard is None else shard.gather_row_parts(row_parts)
                 backend.combine_chunk(prob, parts_all, y, r0, n, workspace)
                 if want_grad:
-                    backend.dz_chunk(prob, y, r0, n, workspace)
+                    backend.dz_chunk(prob, x, y, r0, n, workspace)
                 if side is not None:
                     done = torch.cuda.Event()
                     done.record(side)

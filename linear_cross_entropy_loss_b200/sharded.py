@@ -3,9 +3,9 @@
 Rank g of a process group holds the column slab ``W[:, g*V/G:(g+1)*V/G]`` of the (H, V) weight; ``x``
 and ``y`` are replicated. Per row chunk:
 
-1. every rank runs the forward GEMM on its slab and produces five per-row partials
-   (max, sum exp, target logit, sum exp*z, sum z^2);
-2. ONE small all-gather (``5 * chunk_rows`` floats per rank) makes all partials visible everywhere and a
+1. every rank runs the forward GEMM on its slab and produces six per-row partials
+   (base, sum exp, target logit, sum exp*z, sum z^2, max);
+2. ONE small all-gather (``6 * chunk_rows`` floats per rank) makes all partials visible everywhere and a
    local kernel merges them in rank order into the global log-sum-exp -- bitwise identical on every
    rank, which a max/sum all-reduce pair would not guarantee;
 3. every rank forms dZ for its slab, its own dW slab (no communication) and a partial dx, which is

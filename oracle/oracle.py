@@ -123,9 +123,10 @@ def forward_backward(x, y, W, ignore_index: int = -100, z_regularization: float 
 # must reproduce.
 # ------------------------------------------------------------------------------------------------
 def row_partials(z_slab: np.ndarray, y: np.ndarray, vocab_offset: int, ignore_index: int) -> np.ndarray:
-    """(5, N) partials of one column slab z[:, offset:offset+Vs]:
-    m = max_j z, s = sum_j exp(z - m), t = z[i, y_i] if the slab owns column y_i else 0,
-    u = sum_j exp(z - m) z, q = sum_j z^2."""
+    """(6, N) partials of one column slab z[:, offset:offset+Vs], relative to a per-row base b (here b = max_j z;
+    any finite base describes the same quantities):
+    b, s = sum_j exp(z - b), t = z[i, y_i] if the slab owns column y_i else 0,
+    u = sum_j exp(z - b) z, q = sum_j z^2, max_j z."""
     n, vs = z_slab.shape
     m = z_slab.max(axis=1)
     e = np.exp(z_slab - m[:, None])
@@ -135,19 +136,19 @@ def row_partials(z_slab: np.ndarray, y: np.ndarray, vocab_offset: int, ignore_in
     yl = y - vocab_offset
     own = (y != ignore_index) & (yl >= 0) & (yl < vs)
     t = np.where(own, z_slab[np.arange(n), np.where(own, yl, 0)], 0.0)
-    return np.stack([m, s, t, u, q])
+    return np.stack([m, s, t, u, q, m])
 
 
 def combine_partials(parts: np.ndarray):
-    """parts: (G, 5, N) -> (lse, target_logit, entropy, sq_norm, row_max), each (N,).
-    M = max_g m_g; S = sum_g s_g e^{m_g - M}; lse = M + log S; entropy = lse - (sum_g u_g e^{m_g - M}) / S."""
-    m, s, t, u, q = (parts[:, k, :] for k in range(5))
+    """parts: (G, 6, N) -> (lse, target_logit, entropy, sq_norm, row_max), each (N,).
+    B = max_g b_g; S = sum_g s_g e^{b_g - B}; lse = B + log S; entropy = lse - (sum_g u_g e^{b_g - B}) / S."""
+    m, s, t, u, q, zmax = (parts[:, k, :] for k in range(6))
     M = m.max(axis=0)
     w = np.exp(m - M[None, :])
     S = (s * w).sum(axis=0)
     lse = M + np.log(S)
     ent = lse - (u * w).sum(axis=0) / S
-    return lse, t.sum(axis=0), ent, q.sum(axis=0), M
+    return lse, t.sum(axis=0), ent, q.sum(axis=0), zmax.max(axis=0)
 
 
 # ------------------------------------------------------------------------------------------------

@@ -33,7 +33,7 @@ class FakeBackend:
         yy = y[row0:row0 + rows].numpy()
         parts = oracle.row_partials(z, yy, prob.vocab_offset, prob.ignore_index)
         local0 = row0 % prob.chunk_rows
-        rp = row_parts.view(5, prob.chunk_rows)
+        rp = row_parts.view(6, prob.chunk_rows)
         rp[:, local0:local0 + rows] = torch.from_numpy(parts).float()
         st.setdefault("z", {})[row0] = z
 
@@ -41,7 +41,7 @@ class FakeBackend:
         self.calls.append("combine_chunk")
         st = self.state[workspace.data_ptr()]
         local0 = row0 % prob.chunk_rows
-        parts = row_parts_all.view(prob.world, 5, prob.chunk_rows)[:, :, local0:local0 + rows].double().numpy()
+        parts = row_parts_all.view(prob.world, 6, prob.chunk_rows)[:, :, local0:local0 + rows].double().numpy()
         lse, t, ent, q, m = oracle.combine_partials(parts)
         v = (y[row0:row0 + rows] != prob.ignore_index).numpy()
         st["nll"] += float(((lse - t) * v).sum())
@@ -51,7 +51,7 @@ class FakeBackend:
         st["zmax"] = max(st["zmax"], float(m.max()))
         st.setdefault("lse", {})[row0] = lse
 
-    def dz_chunk(self, prob, y, row0, rows, workspace):
+    def dz_chunk(self, prob, x, y, row0, rows, workspace):
         self.calls.append("dz_chunk")
         st = self.state[workspace.data_ptr()]
         z, lse = st["z"].pop(row0), st["lse"].pop(row0)

@@ -108,6 +108,25 @@ def test_peaked_softmax_large_logit_scale():
     check_against_oracle(x, y, W, torch.bfloat16, ignore=-1, scale=16.0, zreg=1e-3)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_conditional_rerun_when_logits_leave_the_reference_range(dtype):
+    # bf16 / fp32 slabs hold exp(z - 0) first; rows whose max logit is beyond +-60 make the chunk run again with
+    # reference = row max. scale = 32 puts the row maxima near 100 in the first chunk's rows only.
+    x, y, W = random_problem(512, 256, 1024, torch.bfloat16, seed=21)
+    x, W = x.to(dtype), W.to(dtype)     # bf16-representable values: exact as TF32 operands too
+    x[256:] *= 0.25                     # second chunk stays inside the range: no re-run there
+    check_against_oracle(x, y, W, dtype, ignore=-1, scale=32.0, zreg=1e-4, chunk=256)
+
+
+def test_conditional_rerun_on_the_underflow_side():
+    g = torch.Generator().manual_seed(22)
+    x = (torch.rand(256, 256, generator=g) + 0.5).bfloat16()
+    W = (-(torch.rand(256, 512, generator=g)) * 0.8).bfloat16()      # every logit is near -100
+    y = torch.randint(0, 512, (256,), generator=g)
+    got, dxn, dWn, ref = check_against_oracle(x, y, W, torch.bfloat16, chunk=128)
+    assert ref.logit_max < -60
+
+
 def test_strided_rows_of_x_and_w_are_read_in_place():
     x, y, W = random_problem(256, 512, 1024, torch.float16, seed=10)
     xd = x.cuda()[:, :256]            # row stride 512, 256 columns used

@@ -30,7 +30,7 @@ def test_emulated_shards_on_one_gpu(world):
                              ignore_index=-1, world=world, dtype=_native.DTYPE_BF16, monitoring=1, want_grad=1,
                              logit_scale=0.5, z_regularization=1e-3) for g in range(world)]
     ws = [torch.empty(be.workspace_bytes(p), dtype=torch.uint8, device="cuda") for p in probs]
-    parts = torch.empty(world, 5 * chunk, dtype=torch.float32, device="cuda")
+    parts = torch.empty(world, 6 * chunk, dtype=torch.float32, device="cuda")
     dxs = [torch.zeros(N, H, dtype=torch.float32, device="cuda") for _ in range(world)]
     dWs = [torch.empty(H, vl, dtype=torch.float32, device="cuda") for _ in range(world)]
     outs = [torch.empty(5, dtype=torch.float32, device="cuda") for _ in range(world)]
@@ -41,7 +41,7 @@ def test_emulated_shards_on_one_gpu(world):
             be.forward_chunk(probs[g], xd, slabs[g], yd, row0, chunk, ws[g], parts[g])
         for g in range(world):
             be.combine_chunk(probs[g], parts, yd, row0, chunk, ws[g])
-            be.dz_chunk(probs[g], yd, row0, chunk, ws[g])
+            be.dz_chunk(probs[g], xd, yd, row0, chunk, ws[g])
             be.dx_chunk(probs[g], slabs[g], row0, chunk, ws[g], dxs[g])
             be.dw_chunk(probs[g], xd, row0, chunk, ws[g], dWs[g], row0 == 0, None)
     for g in range(world):

@@ -66,6 +66,7 @@ def test_shard_partials_combine_to_the_full_row_statistics(shards):
     vs = 80 // shards
     parts = np.stack([oracle.row_partials(z[:, g * vs:(g + 1) * vs], y, g * vs, -1) for g in range(shards)])
     lse, t, ent, q, m = oracle.combine_partials(parts)
+    assert parts.shape[1] == 6
     full = oracle.forward_backward(x, y, W, -1, 0.0, 0.9, want_grad=False)
     np.testing.assert_allclose(lse, full.lse, atol=1e-13)
     valid = y != -1
