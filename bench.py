@@ -34,9 +34,12 @@ METRIC = "fwd+bwd TFLOP/s (6NHV/t)"
 PUBLISHED_BF16_DEFAULT_TFLOPS = 86.75
 # fallback roofline denominators when the measured-peaks file is absent (earlier measurement on this pool)
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
-# DRAM bytes (read + write) of ONE launch of each contraction kernel at the headline shape, from the ncu captures
-# summarised under profiles/ (null until captured)
-NCU_DRAM_BYTES_PER_LAUNCH = {"fwd": None, "dx": None, "dw": None}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of each contraction kernel, from the ncu
+# capture of the quarter-size case (V=32768) summarised in profiles/lce_gemm_pair_kernel__profile_small_bf16.md:
+# forward 381.9 MB, dx 931.7 MB, dW 406.5 MB. Forward and dx traffic grow in proportion to V; the figures are scaled
+# by V_local / 32768 at run time (only for N_chunk_size=4096, H=2048, which the capture used). dW is not scaled: from
+# the second chunk on it also reads and rewrites the fp32 accumulator, which the one-chunk capture does not contain.
+NCU_DRAM_BYTES_V32768 = {"fwd": 381.9e6, "dx": 931.7e6, "dw": None}
 
 
 def parse_args():
@@ -70,13 +73,16 @@ def load_peaks():
 # clocks
 # ---------------------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi polling in the background; only the samples taken inside [mark_start, mark_end] count."""
+
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
         self.proc = None
+        self.t0 = self.t1 = None
 
     def start(self):
         try:
@@ -85,6 +91,20 @@ class ClockSampler:
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
+
+    def mark_start(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
+    @staticmethod
+    def _parse_time(text):
+        import datetime
+        try:
+            return datetime.datetime.strptime(text.strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
 
     def stop(self):
         if self.proc is None:
@@ -99,15 +119,18 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.splitlines():
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
+            if len(parts) < 10:
+                continue
+            ts = self._parse_time(parts[0])
+            if ts is not None and self.t0 is not None and self.t1 is not None and not (self.t0 <= ts <= self.t1 + 0.05):
                 continue
             try:
-                sm.append(float(parts[1]))
-                smax.append(float(parts[2]))
-                power.append(float(parts[3]))
+                sm.append(float(parts[2]))
+                smax.append(float(parts[3]))
+                power.append(float(parts[4]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[5:9]):
+            for name, val in zip(names, parts[6:10]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
@@ -265,27 +288,30 @@ def main():
         return t.item()
 
     # ---- device-resident throughput -----------------------------------------------------------------
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    if rank == 0:
+        sampler.start()   # started before the warm-up so that it is polling by the time the timed region begins
     for _ in range(max(3, args.warmup)):
         fwd_bwd(x, y)
     barrier()
     torch.cuda.reset_peak_memory_stats()
     mem_before = torch.cuda.memory_allocated()
-    sampler = ClockSampler(physical_gpu_index(local_rank))
-    sampler.start()
     _native.profile_read()
     _native.profile_enable(True)
     launches_before = _native.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark_start()
     e0.record()
     for _ in range(args.steps):
         loss = fwd_bwd(x, y)
     e1.record()
     barrier()
+    sampler.mark_end()
     launches = _native.launch_count() - launches_before
     _native.profile_enable(False)
     kernel_ms, kernel_launches = _native.profile_read()
-    clocks = sampler.stop()
+    clocks = sampler.stop() if rank == 0 else None
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_per_step = ms_total / args.steps
     peak_extra = torch.cuda.max_memory_allocated() - mem_before
@@ -333,10 +359,13 @@ def main():
     roofline = None
     if dominant is not None:
         achieved = kernels[dominant]["tflops"]
+        base = NCU_DRAM_BYTES_V32768.get(dominant)
+        traffic = (base * v_local / 32768.0) if (base and cfg.H == 2048 and min(cfg.N, cfg.N_chunk_size) == 4096) \
+            else None
         roofline = {"bound": "tensor", "kernel": f"lce_gemm_kernel[{dominant}]", "achieved": achieved,
                     "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved / peak_tflops,
                     "peak_source": f"{peak_source} cuBLAS bf16 GEMM, sustained",
-                    "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(dominant),
+                    "traffic": traffic,
                     "flops_per_launch": kernels[dominant]["flops_per_launch"], "kernels": kernels,
                     "whole_step_frac": (value / world) / peak_tflops}
 
