@@ -150,6 +150,30 @@ int lce_grad_scale_cast(const void* src, int32_t src_dtype, int64_t src_ld, void
  * (LCE_ERR_DEVICE_TIMEOUT if a bounded in-kernel wait ran out). Debugging / tests. */
 int lce_read_status(void* workspace, void* stream);
 
+/* ---- evaluation without a workspace ---------------------------------------------------------------
+ * lce_eval_loss_static computes the five output scalars of a forward-only pass (out5 as in lce_finalize)
+ * for callers that cannot hand the library a workspace because they cannot allocate device memory at the
+ * point of the call: a latency-critical loop that must not pay cudaMalloc's implicit device
+ * synchronisation, an inference-server plugin that is only given its input and output buffers, an
+ * evaluation hook running after the framework's memory pool has claimed all device memory. Its scratch (per-tile softmax statistics, per-row partials, accumulators)
+ * is a fixed LCE_STATIC_SCRATCH_BYTES array inside the library's device image: every GPU that loads the
+ * library holds it until the process exits, and the entry point calls no cudaMalloc, cudaFree or other
+ * allocating routine. The caller still passes x, weight, labels and out5 (device pointers).
+ *   - p: n_rows_total, hidden, vocab_local, dtype, ignore_index, logit_scale, z_regularization and
+ *     monitoring are used; chunk_rows, world, vocab_offset and want_grad are ignored (forward only,
+ *     unsharded; rows are processed in the largest chunks whose statistics fit the scratch).
+ *   - LCE_ERR_TOO_LARGE if not even 128 rows fit (vocab_local beyond about 2 million columns); the other
+ *     shape rules are those of lce_forward_chunk.
+ *   - The first call on each device resolves the scratch array's device address (cudaGetSymbolAddress) and
+ *     sets kernel attributes; make that first call outside of any stream capture.
+ *   - All calls share the one array, which keeps the previous call's contents: every accumulator is cleared
+ *     at the start of a call, everything else is rewritten before it is read. Two calls that overlap on the
+ *     GPU (different streams, or different host threads on one device) race on it; serialise them.
+ * It has no counterpart in the reference. */
+#define LCE_STATIC_SCRATCH_BYTES (8u << 20)
+int lce_eval_loss_static(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
+                         const int64_t* labels, float* out5, void* stream);
+
 /* ---- measurement ------------------------------------------------------------------------------
  * With profiling enabled, a CUDA event pair is recorded on the launching stream around each of the
  * three tensor-core contractions (0: logits z = x W, 1: dx = dZ W^T, 2: dW = x^T dZ).

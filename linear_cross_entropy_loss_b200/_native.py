@@ -115,6 +115,7 @@ SIGNATURES = {
     "lce_finalize": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _vp, _vp]),
     "lce_grad_scale_cast": (ctypes.c_int, [_vp, _i32, _i64, _vp, _i32, _i64, _i64, _i64, _vp, _vp]),
     "lce_read_status": (ctypes.c_int, [_vp, _vp]),
+    "lce_eval_loss_static": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _vp, _vp, _vp]),
     "lce_set_gemm_variant": (ctypes.c_int, [_i32]),
     "lce_profile_enable": (ctypes.c_int, [_i32]),
     "lce_profile_read": (ctypes.c_int, [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]),

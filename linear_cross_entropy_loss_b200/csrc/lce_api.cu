@@ -825,3 +825,71 @@ int lce_debug_gemm(int32_t dtype, int32_t a_mn_major, int32_t b_mn_major, const 
 }
 
 }  // extern "C"
+
+// ================================================================================================
+// Loss evaluation without any caller-provided scratch (lce_eval_loss_static)
+// ================================================================================================
+namespace {
+
+// Scratch of the allocation-free entry point. It lives in the library's device image, so every GPU that
+// loads the library holds these 8 MiB until the process exits. In host code this name is only a handle
+// for cudaGetSymbolAddress -- it is NOT a device address and must never be handed to a kernel as is.
+static __device__ __align__(256) unsigned char g_static_scratch[LCE_STATIC_SCRATCH_BYTES];
+
+std::mutex g_static_mutex;
+void* g_static_scratch_ptr[kMaxDevices] = {};  // device address of g_static_scratch, per device
+
+// Resolves (once per device, with that device current) the device address of the scratch array.
+int static_scratch_address(void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return LCE_ERR_CUDA;
+  if (dev < 0 || dev >= kMaxDevices) return LCE_ERR_UNSUPPORTED_DEVICE;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return LCE_ERR_CUDA;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return LCE_OK;
+}
+
+}  // namespace
+
+extern "C" int lce_eval_loss_static(const lce_problem* p_in, const void* x, int64_t x_ld, const void* weight,
+                                    int64_t w_ld, const int64_t* labels, float* out5, void* stream) {
+  if (p_in == nullptr || !x || !weight || !labels || !out5) return LCE_ERR_INVALID_ARGUMENT;
+  // forward only, unsharded; the chunk length is chosen here so that everything fits the fixed scratch
+  lce_problem p = *p_in;
+  p.want_grad = 0;
+  p.world = 1;
+  p.vocab_offset = 0;
+  p.chunk_rows = p.n_rows_total < BLOCK_M ? p.n_rows_total : BLOCK_M;  // provisional, for the shape checks
+  int v = validate_problem(&p);
+  if (v != LCE_OK) return v;
+  const int sms = sm_count_or_default();
+  long long best = 0;
+  for (long long rows = BLOCK_M; rows <= p.n_rows_total; rows += BLOCK_M) {
+    p.chunk_rows = rows;
+    const size_t need = align_up(layout_workspace(&p, nullptr, sms).total, 256) + (size_t)ROW_PARTS * rows * sizeof(float);
+    if (need > (size_t)LCE_STATIC_SCRATCH_BYTES) break;
+    best = rows;
+  }
+  if (best == 0) return LCE_ERR_TOO_LARGE;  // even 128 rows of statistics exceed the fixed scratch: vocab too large
+  p.chunk_rows = best;
+
+  void* scratch = nullptr;
+  if ((v = static_scratch_address(&scratch)) != LCE_OK) return v;
+  const size_t ws_bytes = align_up(layout_workspace(&p, nullptr, sms).total, 256);
+  float* parts = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + ws_bytes);
+
+  // lce_begin clears every accumulator the pass sums into; all other scratch is written before it is read
+  if ((v = lce_begin(&p, labels, scratch, stream)) != LCE_OK) return v;
+  for (long long row0 = 0; row0 < p.n_rows_total; row0 += p.chunk_rows) {
+    const long long rows = (p.n_rows_total - row0 < p.chunk_rows) ? p.n_rows_total - row0 : p.chunk_rows;
+    if ((v = lce_forward_chunk(&p, x, x_ld, weight, w_ld, labels, row0, rows, scratch, parts, stream)) != LCE_OK)
+      return v;
+    if ((v = lce_combine_chunk(&p, parts, labels, row0, rows, scratch, stream)) != LCE_OK) return v;
+  }
+  return lce_finalize(&p, scratch, out5, stream);
+}
