@@ -50,8 +50,8 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--config", default="headline_bf16")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
-    ap.add_argument("--gemm-variant", type=int, default=0, choices=[0, 1],
-                    help="0: CTA-pair tensor-core kernels (default), 1: single-CTA kernels (A/B measurement)")
+    ap.add_argument("--gemm-variant", type=int, default=0, choices=[0, 1, 2, 3],
+                    help="A/B measurement bits: 1 = single-CTA kernels instead of CTA pairs, 2 = dx tiles M-first")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1, rank 0)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU work of the baseline leg")
     ap.add_argument("--ref-budget", type=float, default=100.0,
@@ -213,7 +213,7 @@ def config_dict(cfg, n_gpus, args):
         "N": cfg.N, "H": cfg.H, "V": cfg.V, "N_chunk_size": cfg.N_chunk_size,
         "vocab_sharding": f"{n_gpus} x {cfg.V // n_gpus} columns" if n_gpus > 1 else "none",
         "l2": "inputs larger than L2 (the weight alone is >= 512 MiB per GPU); no explicit flush",
-        "gemm_variant": "single-CTA 128x256 tiles" if getattr(args, "gemm_variant", 0) == 1 else "CTA-pair 256x256 tiles",
+        "gemm_variant": "single-CTA 128x256 tiles" if getattr(args, "gemm_variant", 0) & 1 else "CTA-pair 256x256 tiles",
     }
 
 

@@ -184,9 +184,9 @@ int lce_profile_enable(int32_t enable);
 int lce_profile_read(double* ms3, long long* launches3);
 
 /* ---- diagnostics ------------------------------------------------------------------------------
- * lce_set_gemm_variant: 0 (default) runs the contractions on CTA pairs (cta_group::2, 256 x 256 tiles)
- * whenever the row count allows it; 1 forces the single-CTA kernel (128 x 256 tiles) everywhere.
- * Process-wide; for A/B measurements and tests. No counterpart in the reference. */
+ * lce_set_gemm_variant: bit mask, 0 by default. Bit 0 forces the single-CTA kernel (128 x 256 tiles) everywhere
+ * instead of CTA pairs (cta_group::2, 256 x 256 tiles); bit 1 makes the dx contraction walk its tiles M-first
+ * instead of N-first. Process-wide; for A/B measurements and tests. No counterpart in the reference. */
 int lce_set_gemm_variant(int32_t variant);
 
 /*

@@ -59,11 +59,12 @@ struct GemmShared {
 constexpr size_t kGemmSmemBytes = size_t(kStages) * kStageBytes + 1024 /*alignment slack*/ + sizeof(GemmShared);
 
 struct GemmParams {
-  // tile grid; units = splits * n_tiles * m_tiles, m fastest
+  // tile grid; units = splits * n_tiles * m_tiles, walked in the order n_fastest selects
   int m_tiles;
   int n_tiles;
   int splits;
   int k_blocks;  // K-blocks (128 bytes of K each) per split
+  int n_fastest; // 0: consecutive units walk M first (then N, then the K-split); 1: they walk N first
   // element offsets added to the tensor-map coordinates
   int a_mn0, a_k0, b_mn0, b_k0;
 
@@ -146,42 +147,39 @@ struct SlabElem<KIND_TF32> {
   using type = float;
 };
 
+// 32 consecutive elements of one output row, written as full 32-byte sectors (dst is 32-byte aligned).
 __device__ __forceinline__ void store_slab_chunk(__half* dst, const float (&e)[32]) {
-  uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    __half2 h0 = __floats2half2_rn(e[8 * i + 0], e[8 * i + 1]);
-    __half2 h1 = __floats2half2_rn(e[8 * i + 2], e[8 * i + 3]);
-    __half2 h2 = __floats2half2_rn(e[8 * i + 4], e[8 * i + 5]);
-    __half2 h3 = __floats2half2_rn(e[8 * i + 6], e[8 * i + 7]);
-    uint4 v;
-    v.x = *reinterpret_cast<uint32_t*>(&h0);
-    v.y = *reinterpret_cast<uint32_t*>(&h1);
-    v.z = *reinterpret_cast<uint32_t*>(&h2);
-    v.w = *reinterpret_cast<uint32_t*>(&h3);
-    d4[i] = v;
+  for (int i = 0; i < 2; ++i) {
+    uint32_t v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      __half2 h = __floats2half2_rn(e[16 * i + 2 * k], e[16 * i + 2 * k + 1]);
+      v[k] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    st_global_256(dst + 16 * i, v);
   }
 }
 __device__ __forceinline__ void store_slab_chunk(__nv_bfloat16* dst, const float (&e)[32]) {
-  uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    __nv_bfloat162 h0 = __floats2bfloat162_rn(e[8 * i + 0], e[8 * i + 1]);
-    __nv_bfloat162 h1 = __floats2bfloat162_rn(e[8 * i + 2], e[8 * i + 3]);
-    __nv_bfloat162 h2 = __floats2bfloat162_rn(e[8 * i + 4], e[8 * i + 5]);
-    __nv_bfloat162 h3 = __floats2bfloat162_rn(e[8 * i + 6], e[8 * i + 7]);
-    uint4 v;
-    v.x = *reinterpret_cast<uint32_t*>(&h0);
-    v.y = *reinterpret_cast<uint32_t*>(&h1);
-    v.z = *reinterpret_cast<uint32_t*>(&h2);
-    v.w = *reinterpret_cast<uint32_t*>(&h3);
-    d4[i] = v;
+  for (int i = 0; i < 2; ++i) {
+    uint32_t v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(e[16 * i + 2 * k], e[16 * i + 2 * k + 1]);
+      v[k] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    st_global_256(dst + 16 * i, v);
   }
 }
 __device__ __forceinline__ void store_slab_chunk(float* dst, const float (&e)[32]) {
-  float4* d4 = reinterpret_cast<float4*>(dst);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) d4[i] = make_float4(e[4 * i + 0], e[4 * i + 1], e[4 * i + 2], e[4 * i + 3]);
+  for (int i = 0; i < 4; ++i) {
+    uint32_t v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = __float_as_uint(e[8 * i + k]);
+    st_global_256(dst + 8 * i, v);
+  }
 }
 
 // Forward epilogue. For its row i and this tile's 256 columns j (z = scale * acc):
@@ -339,14 +337,13 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr
     tmem_ld_wait();
     float r[32];
     if (p.accumulate) {
-      const float4* s4 = reinterpret_cast<const float4*>(dst + c * 32);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float4 o = s4[i];
-        r[4 * i + 0] = fmaf(coef, __uint_as_float(v[4 * i + 0]), o.x);
-        r[4 * i + 1] = fmaf(coef, __uint_as_float(v[4 * i + 1]), o.y);
-        r[4 * i + 2] = fmaf(coef, __uint_as_float(v[4 * i + 2]), o.z);
-        r[4 * i + 3] = fmaf(coef, __uint_as_float(v[4 * i + 3]), o.w);
+      for (int i = 0; i < 4; ++i) {
+        uint32_t o[8];
+        ld_global_256(dst + c * 32 + 8 * i, o);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          r[8 * i + k] = fmaf(coef, __uint_as_float(v[8 * i + k]), __uint_as_float(o[k]));
       }
     } else {
 #pragma unroll
@@ -427,8 +424,8 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
         const int split = unit / tiles_mn;
         const int rem = unit - split * tiles_mn;
-        const int n_blk = rem / p.m_tiles;
-        const int m_blk = rem - n_blk * p.m_tiles;
+        const int n_blk = p.n_fastest ? rem % p.n_tiles : rem / p.m_tiles;
+        const int m_blk = p.n_fastest ? rem / p.n_tiles : rem - n_blk * p.m_tiles;
         const int a_mn = p.a_mn0 + m_blk * BLOCK_M;
         const int b_mn = p.b_mn0 + n_blk * BLOCK_N;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
@@ -518,8 +515,8 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
       const int split = unit / tiles_mn;
       const int rem = unit - split * tiles_mn;
-      const int n_blk = rem / p.m_tiles;
-      const int m_blk = rem - n_blk * p.m_tiles;
+      const int n_blk = p.n_fastest ? rem % p.n_tiles : rem / p.m_tiles;
+      const int m_blk = p.n_fastest ? rem / p.n_tiles : rem - n_blk * p.m_tiles;
       if (!mbar_wait_warp(&sh->acc_full[acc], acc_phase, abort_flag)) {
         if (lane == 0) atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_EPILOGUE);
         break;
@@ -664,8 +661,8 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       for (int unit = cluster_id; ok && unit < units; unit += n_clusters) {
         const int split = unit / tiles_mn;
         const int rem = unit - split * tiles_mn;
-        const int n_blk = rem / p.m_tiles;
-        const int m_blk = rem - n_blk * p.m_tiles;
+        const int n_blk = p.n_fastest ? rem % p.n_tiles : rem / p.m_tiles;
+        const int m_blk = p.n_fastest ? rem / p.n_tiles : rem - n_blk * p.m_tiles;
         const int a_mn = p.a_mn0 + m_blk * PAIR_M + int(rank) * BLOCK_M;
         const int b_mn = p.b_mn0 + n_blk * BLOCK_N + int(rank) * HALF_N;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
@@ -760,8 +757,8 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     for (int unit = cluster_id; unit < units; unit += n_clusters) {
       const int split = unit / tiles_mn;
       const int rem = unit - split * tiles_mn;
-      const int n_blk = rem / p.m_tiles;
-      const int m_blk = rem - n_blk * p.m_tiles;
+      const int n_blk = p.n_fastest ? rem % p.n_tiles : rem / p.m_tiles;
+      const int m_blk = p.n_fastest ? rem / p.n_tiles : rem - n_blk * p.m_tiles;
       const int m_blk128 = m_blk * 2 + int(rank);  // this CTA's 128-row block
       if (!mbar_wait_warp(&sh->acc_full[acc], acc_phase, abort_flag)) {
         if (lane == 0) atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_EPILOGUE);

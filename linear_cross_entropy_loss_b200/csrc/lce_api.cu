@@ -16,7 +16,8 @@ namespace {
 using namespace lce;
 
 std::atomic<long long> g_launches{0};
-// 0: CTA-pair kernel whenever the tile grid allows it, 1: always the single-CTA kernel (lce_set_gemm_variant)
+// bit 0: always the single-CTA kernel instead of the CTA-pair kernel; bit 1: dx walks its tiles M-first like the
+// other two contractions instead of N-first (lce_set_gemm_variant; both bits are for A/B measurements)
 std::atomic<int> g_gemm_variant{0};
 
 // ------------------------------------------------------------------------------------------------
@@ -274,7 +275,7 @@ struct ProfScope {
 // 256 x 256 tiles, one per cluster of two CTAs, each CTA loading 128 rows of A and 128 of the 256 B columns.
 // The B tensor map must be built for the variant that will run (rows_of_b_tile).
 bool use_pair_kernel(long long m_tiles128, int sms) {
-  return (m_tiles128 % 2 == 0) && sms >= 2 && g_gemm_variant.load(std::memory_order_relaxed) == 0;
+  return (m_tiles128 % 2 == 0) && sms >= 2 && (g_gemm_variant.load(std::memory_order_relaxed) & 1) == 0;
 }
 int rows_of_b_tile(bool pair) { return pair ? BLOCK_N / 2 : BLOCK_N; }
 
@@ -572,6 +573,9 @@ int lce_dx_chunk(const lce_problem* p, const void* weight, int64_t w_ld, int64_t
   gp.splits = w.dx_splits;
   gp.k_blocks = (int)(p->vocab_local * es / 128 / w.dx_splits);
   gp.a_mn0 = (int)local0;
+  // N-first: the units in flight at one time then cover all H tiles of a few row blocks, so each slab row block is
+  // streamed from DRAM once and only the (smaller) weight is re-read per group of row blocks
+  gp.n_fastest = (g_gemm_variant.load(std::memory_order_relaxed) & 2) ? 0 : 1;
   gp.out = part;
   gp.out_ld = p->hidden;
   gp.out_split_stride = (long long)p->chunk_rows * p->hidden;
@@ -619,9 +623,10 @@ int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0
   const bool need_acc = !(first && dweight_final != nullptr);
   if (need_acc && (!dweight_acc || dw_ld < p->vocab_local)) return LCE_ERR_INVALID_ARGUMENT;
   if (dweight_final && dwf_ld < p->vocab_local) return LCE_ERR_INVALID_ARGUMENT;
-  if (dweight_acc && ((reinterpret_cast<uintptr_t>(dweight_acc) & 15u) != 0 || (dw_ld & 3) != 0))
+  // the epilogue moves 32-byte sectors
+  if (dweight_acc && ((reinterpret_cast<uintptr_t>(dweight_acc) & 31u) != 0 || (dw_ld & 7) != 0))
     return LCE_ERR_MISALIGNED;
-  if (dweight_final && ((reinterpret_cast<uintptr_t>(dweight_final) & 15u) != 0 || (dwf_ld & 7) != 0))
+  if (dweight_final && ((reinterpret_cast<uintptr_t>(dweight_final) & 31u) != 0 || (dwf_ld & 15) != 0))
     return LCE_ERR_MISALIGNED;
   int sms = 0;
   if ((v = ensure_device(&sms)) != LCE_OK) return v;
@@ -751,7 +756,7 @@ int lce_read_status(void* workspace, void* stream) {
 }
 
 int lce_set_gemm_variant(int32_t variant) {
-  if (variant != 0 && variant != 1) return LCE_ERR_INVALID_ARGUMENT;
+  if (variant < 0 || variant > 3) return LCE_ERR_INVALID_ARGUMENT;
   g_gemm_variant.store(variant, std::memory_order_relaxed);
   return LCE_OK;
 }
