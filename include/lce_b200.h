@@ -19,8 +19,9 @@
  *   - W is stored (hidden, vocab) with the vocab index contiguous, like the reference's
  *     transposed nn.Linear weight (ops.py:913).
  *
- * Shapes: rows per chunk % 128 == 0, hidden % 256 == 0, vocab_local % 256 == 0
- * (the reference asserts N % 512, V % 4096, H % 256: ops.py:689-691).
+ * Shapes: any number of rows; hidden % 8 == 0 and vocab_local % 8 == 0 (rows of x and W start on 16-byte
+ * boundaries); chunk_rows % 128 == 0. The kernels work on 128 x 256 tiles: what hangs over the edges is
+ * zero-filled on load and masked on store. (The reference asserts N % 512, V % 4096, H % 256: ops.py:689-691.)
  */
 #ifndef LCE_B200_H
 #define LCE_B200_H
@@ -50,7 +51,7 @@ extern "C" {
 /* One problem description shared by all calls of one forward+backward pass. */
 typedef struct lce_problem {
   int64_t n_rows_total;   /* N = B*S, all chunks                                  */
-  int64_t chunk_rows;     /* rows per chunk, min(N, N_chunk_size) (ops.py:687)    */
+  int64_t chunk_rows;     /* rows per chunk: min(N, N_chunk_size) (ops.py:687) rounded up to a multiple of 128 */
   int64_t hidden;         /* H = in_features                                       */
   int64_t vocab_local;    /* columns of W held by this rank (V when not sharded)  */
   int64_t vocab_offset;   /* class id of local column 0 (0 when not sharded)      */
@@ -92,7 +93,8 @@ int lce_begin(const lce_problem* p, const int64_t* labels, void* workspace, void
 
 /* x: [n_rows_total, hidden] with row stride x_ld elements; weight: [hidden, vocab_local] with row
  * stride w_ld elements; labels: [n_rows_total]. Processes rows [row0, row0 + rows), which must lie
- * inside one chunk (chunks start at multiples of chunk_rows) and be 128-aligned.
+ * inside one chunk (chunks start at multiples of chunk_rows); row0 % 128 == 0, and rows % 128 == 0 unless
+ * the call ends with the last row of the problem.
  * row_parts_local: float[LCE_ROW_PARTS * chunk_rows] output (this rank's per-row partials). */
 int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
                       const int64_t* labels, int64_t row0, int64_t rows, void* workspace,

@@ -328,16 +328,19 @@ struct Vec8<float> {
 template <typename T>
 __global__ void __launch_bounds__(256)
 dz_transform_kernel(T* __restrict__ slab, long long slab_ld, const float* __restrict__ tile_max,
-                    const float* __restrict__ lse, const long long* __restrict__ labels, int rows, int n_tiles,
-                    long long stat_ld, long long ignore_index, long long vocab_offset, float z_regularization) {
+                    const float* __restrict__ lse, const long long* __restrict__ labels, int rows, int rows_valid,
+                    int n_tiles, long long stat_ld, long long ignore_index, long long vocab_offset,
+                    float z_regularization) {
+  // rows: multiple of 128 (slab rows to rewrite); rows >= rows_valid are padding and become zero
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long items = (long long)(rows / 8) * n_tiles;
   for (long long item = blockIdx.x; item < items; item += gridDim.x) {
     const int tile = (int)(item % n_tiles);
     const int r = (int)(item / n_tiles) * 8 + warp;
-    const long long yv = labels[r];
+    const bool exists = r < rows_valid;
+    const long long yv = exists ? labels[r] : ignore_index;
     const bool valid = (yv != ignore_index);
-    const float lse_r = lse[r];
+    const float lse_r = exists ? lse[r] : 0.f;
     const float coef =
         valid ? __expf(tile_max[(long long)tile * stat_ld + r] - lse_r) * (1.f + 2.f * z_regularization * lse_r)
               : 0.f;
@@ -388,12 +391,15 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 row_finish_kernel(const T* __restrict__ x, long long x_ld, T* __restrict__ xs, long long xs_ld, int hidden,
                   T* __restrict__ slab, long long slab_ld, const float* __restrict__ ref, const float* __restrict__ lse,
-                  const long long* __restrict__ labels, long long ignore_index, long long vocab_offset,
-                  long long vocab_local, float z_regularization, float* __restrict__ row_coef) {
+                  const long long* __restrict__ labels, int rows_valid, long long ignore_index,
+                  long long vocab_offset, long long vocab_local, float z_regularization,
+                  float* __restrict__ row_coef) {
+  // grid = rows rounded up to 128: blocks r >= rows_valid are padding rows (factor 0, zero xs row)
   const int r = blockIdx.x;
-  const long long yv = labels[r];
+  const bool exists = r < rows_valid;
+  const long long yv = exists ? labels[r] : ignore_index;
   const bool valid = (yv != ignore_index);
-  const float l = lse[r];
+  const float l = exists ? lse[r] : 0.f;
   float C = valid ? __expf(ref[r] - l) * (1.f + 2.f * z_regularization * l) : 0.f;
   if (valid && fabsf(C) < 1e-30f) C = (C < 0.f) ? -1e-30f : 1e-30f;  // keeps 1 / C finite
   if (threadIdx.x == 0) {
@@ -406,13 +412,18 @@ row_finish_kernel(const T* __restrict__ x, long long x_ld, T* __restrict__ xs, l
   }
   const T* src = x + (long long)r * x_ld;
   T* dst = xs + (long long)r * xs_ld;
-  for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+  for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {  // hidden % 8 == 0
     Vec8<T> v;
-    v.load(src + c);
     float f[8];
-    v.to_float(f);
+    if (exists) {
+      v.load(src + c);
+      v.to_float(f);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) f[k] *= C;
+      for (int k = 0; k < 8; ++k) f[k] *= C;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] = 0.f;
+    }
     v.from_float(f);
     v.store(dst + c);
   }
@@ -421,16 +432,16 @@ row_finish_kernel(const T* __restrict__ x, long long x_ld, T* __restrict__ xs, l
 // dx[r, h] = sum_s part[s][r][h]  (fixed order s = 0, 1, ...), cast to T. cols % 4 == 0.
 template <typename T>
 __global__ void __launch_bounds__(256)
-dx_reduce_kernel(const float* __restrict__ part, int splits, long long split_stride, int rows, int cols,
-                 T* __restrict__ dx, long long dx_ld) {
+dx_reduce_kernel(const float* __restrict__ part, int splits, long long split_stride, long long part_ld, int rows,
+                 int cols, T* __restrict__ dx, long long dx_ld) {
   const long long quads = (long long)rows * (cols / 4);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < quads;
        i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / (cols / 4);
     const int c = (int)(i % (cols / 4)) * 4;
-    float4 acc = *reinterpret_cast<const float4*>(part + r * cols + c);
+    float4 acc = *reinterpret_cast<const float4*>(part + r * part_ld + c);
     for (int s = 1; s < splits; ++s) {
-      const float4 v = *reinterpret_cast<const float4*>(part + (long long)s * split_stride + r * cols + c);
+      const float4 v = *reinterpret_cast<const float4*>(part + (long long)s * split_stride + r * part_ld + c);
       acc.x += v.x;
       acc.y += v.y;
       acc.z += v.z;

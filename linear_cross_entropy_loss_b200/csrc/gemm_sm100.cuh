@@ -77,6 +77,9 @@ struct GemmParams {
   const float* out_div;
   void* out_final;             // when non-null the result goes here, converted to the input element type,
   long long out_final_ld;      // instead of back to `out` (last accumulation step of dW)
+  int out_rows;                // rows / columns of the output that exist; tiles may hang over both edges
+  int out_cols;
+  int out_vector_ok;           // 1: out, out_final and their strides allow 32-byte accesses
 
   // ---- EPI_FWD: softmax statistics + exp slab
   void* slab;                  // [rows, slab_ld] in the input element type: exp(z - tile row max)
@@ -88,7 +91,9 @@ struct GemmParams {
   float* tile_sq;              //                    sum_j z^2                  (monitoring)
   long long stat_ld;
   float* target_logit;         // [rows] z[i, y_i], written by the one tile that holds column y_i
-  const long long* labels;     // [rows]
+  const long long* labels;     // [rows_valid]
+  int rows_valid;              // rows of this call that exist (the last 128-row tile may be partly padding)
+  int cols_valid;              // vocabulary columns that exist (the last 256-column tile may be partly padding)
   long long ignore_index;
   long long vocab_offset;      // global class id of local column 0
   float scale;                 // logit scale (> 0)
@@ -147,6 +152,15 @@ struct SlabElem<KIND_TF32> {
   using type = float;
 };
 
+template <typename T>
+__device__ __forceinline__ T cast_elem(float v);
+template <>
+__device__ __forceinline__ float cast_elem<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half cast_elem<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 cast_elem<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
 // 32 consecutive elements of one output row, written as full 32-byte sectors (dst is 32-byte aligned).
 __device__ __forceinline__ void store_slab_chunk(__half* dst, const float (&e)[32]) {
 #pragma unroll
@@ -190,12 +204,14 @@ __device__ __forceinline__ void store_slab_chunk(float* dst, const float (&e)[32
 // exponentials normalised per tile; the slab is rescaled to the row's log-sum-exp afterwards.
 template <int kKind, bool kMonitor>
 __device__ __forceinline__ void epilogue_forward_tilemax(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk,
-                                                 int row_in_tile) {
+                                                         int row_in_tile) {
   using Elem = typename SlabElem<kKind>::type;
   const long long r = (long long)m_blk * BLOCK_M + row_in_tile;
-  const long long yv = p.labels[r];
+  const bool row_ok = r < p.rows_valid;                       // padding rows have no label and store no statistics
+  const long long yv = row_ok ? p.labels[r] : p.ignore_index;
   const long long ycol_ll = yv - p.vocab_offset - (long long)n_blk * BLOCK_N;
   const int ycol = (yv != p.ignore_index && ycol_ll >= 0 && ycol_ll < BLOCK_N) ? (int)ycol_ll : -1;
+  const int ncols = min(BLOCK_N, p.cols_valid - n_blk * BLOCK_N);  // columns of this tile that exist (>= 1)
 
   float mx = -INFINITY, sq = 0.f, tv = 0.f;
 #pragma unroll 1
@@ -203,11 +219,14 @@ __device__ __forceinline__ void epilogue_forward_tilemax(const GemmParams& p, ui
     uint32_t v[32];
     tmem_ld_32x32b_x32(taddr + c * 32, v);
     tmem_ld_wait();
+    const int lim = ncols - c * 32;  // >= 32: the whole chunk exists
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       const float f = __uint_as_float(v[i]);
-      mx = fmaxf(mx, f);
-      if (kMonitor) sq = fmaf(f, f, sq);
+      if (i < lim) {
+        mx = fmaxf(mx, f);
+        if (kMonitor) sq = fmaf(f, f, sq);
+      }
     }
     if ((ycol >> 5) == c) {
       const int sel = ycol & 31;
@@ -226,25 +245,28 @@ __device__ __forceinline__ void epilogue_forward_tilemax(const GemmParams& p, ui
     uint32_t v[32];
     tmem_ld_32x32b_x32(taddr + c * 32, v);
     tmem_ld_wait();
+    const int lim = ncols - c * 32;
     float e[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       const float f = __uint_as_float(v[i]);
-      e[i] = fast_exp2(fmaf(f, sl2, neg_m));
+      e[i] = (i < lim) ? fast_exp2(fmaf(f, sl2, neg_m)) : 0.f;  // padding columns hold 0 in the slab
       s += e[i];
-      if (kMonitor) ez = fmaf(e[i], f, ez);
+      if (kMonitor && i < lim) ez = fmaf(e[i], f, ez);
     }
     if (p.store_slab) store_slab_chunk(slab_row + c * 32, e);
   }
 
-  const long long si = (long long)n_blk * p.stat_ld + r;
-  p.tile_max[si] = mx * p.scale;
-  p.tile_sum[si] = s;
-  if (kMonitor) {
-    p.tile_ez[si] = ez * p.scale;
-    p.tile_sq[si] = sq * p.scale * p.scale;
+  if (row_ok) {
+    const long long si = (long long)n_blk * p.stat_ld + r;
+    p.tile_max[si] = mx * p.scale;
+    p.tile_sum[si] = s;
+    if (kMonitor) {
+      p.tile_ez[si] = ez * p.scale;
+      p.tile_sq[si] = sq * p.scale * p.scale;
+    }
+    if (ycol >= 0) p.target_logit[r] = tv * p.scale;
   }
-  if (ycol >= 0) p.target_logit[r] = tv * p.scale;
 }
 
 // Forward epilogue, row-reference mode (bf16 and fp32 slabs, whose exponent range is that of fp32): one pass.
@@ -259,10 +281,12 @@ __device__ __forceinline__ void epilogue_forward_rowref(const GemmParams& p, uin
                                                         int row_in_tile) {
   using Elem = typename SlabElem<kKind>::type;
   const long long r = (long long)m_blk * BLOCK_M + row_in_tile;
-  const long long yv = p.labels[r];
+  const bool row_ok = r < p.rows_valid;                       // padding rows have no label and store no statistics
+  const long long yv = row_ok ? p.labels[r] : p.ignore_index;
   const long long ycol_ll = yv - p.vocab_offset - (long long)n_blk * BLOCK_N;
   const int ycol = (yv != p.ignore_index && ycol_ll >= 0 && ycol_ll < BLOCK_N) ? (int)ycol_ll : -1;
-  const float ref = (p.row_ref != nullptr) ? p.row_ref[r] : 0.f;
+  const int ncols = min(BLOCK_N, p.cols_valid - n_blk * BLOCK_N);  // columns of this tile that exist (>= 1)
+  const float ref = (p.row_ref != nullptr && row_ok) ? p.row_ref[r] : 0.f;
   const float sl2 = p.scale * 1.4426950408889634f;  // scale * log2(e)
   const float neg_ref = -ref * 1.4426950408889634f;
 
@@ -273,16 +297,34 @@ __device__ __forceinline__ void epilogue_forward_rowref(const GemmParams& p, uin
     uint32_t v[32];
     tmem_ld_32x32b_x32(taddr + c * 32, v);
     tmem_ld_wait();
+    const int lim = ncols - c * 32;  // >= 32: the whole chunk exists
     float e[32];
+    if (lim >= 32) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float f = __uint_as_float(v[i]);
-      mx = fmaxf(mx, f);
-      e[i] = fast_exp2(fmaf(f, sl2, neg_ref));
-      s += e[i];
-      if (kMonitor) {
-        ez = fmaf(e[i], f, ez);
-        sq = fmaf(f, f, sq);
+      for (int i = 0; i < 32; ++i) {
+        const float f = __uint_as_float(v[i]);
+        mx = fmaxf(mx, f);
+        e[i] = fast_exp2(fmaf(f, sl2, neg_ref));
+        s += e[i];
+        if (kMonitor) {
+          ez = fmaf(e[i], f, ez);
+          sq = fmaf(f, f, sq);
+        }
+      }
+    } else {  // chunk that hangs over the end of the vocabulary: padding columns count as exp(-inf) = 0
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float f = __uint_as_float(v[i]);
+        e[i] = 0.f;
+        if (i < lim) {
+          mx = fmaxf(mx, f);
+          e[i] = fast_exp2(fmaf(f, sl2, neg_ref));
+          s += e[i];
+          if (kMonitor) {
+            ez = fmaf(e[i], f, ez);
+            sq = fmaf(f, f, sq);
+          }
+        }
       }
     }
     if ((ycol >> 5) == c) {
@@ -294,14 +336,16 @@ __device__ __forceinline__ void epilogue_forward_rowref(const GemmParams& p, uin
     if (p.store_slab) store_slab_chunk(slab_row + c * 32, e);
   }
 
-  const long long si = (long long)n_blk * p.stat_ld + r;
-  p.tile_max[si] = mx * p.scale;
-  p.tile_sum[si] = s;
-  if (kMonitor) {
-    p.tile_ez[si] = ez * p.scale;
-    p.tile_sq[si] = sq * p.scale * p.scale;
+  if (row_ok) {
+    const long long si = (long long)n_blk * p.stat_ld + r;
+    p.tile_max[si] = mx * p.scale;
+    p.tile_sum[si] = s;
+    if (kMonitor) {
+      p.tile_ez[si] = ez * p.scale;
+      p.tile_sq[si] = sq * p.scale * p.scale;
+    }
+    if (ycol >= 0) p.target_logit[r] = tv * p.scale;
   }
-  if (ycol >= 0) p.target_logit[r] = tv * p.scale;
 }
 
 // fp16 slabs are normalised per tile, bf16 / fp32 slabs per row.
@@ -326,33 +370,55 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr
                                              int row_in_tile) {
   using Elem = typename SlabElem<kKind>::type;
   const long long row = (long long)m_blk * BLOCK_M + row_in_tile;
+  const bool row_ok = row < p.out_rows;
+  const int ncols = min(BLOCK_N, p.out_cols - n_blk * BLOCK_N);  // columns of this tile that exist
   float* dst = p.out + (long long)split * p.out_split_stride + row * p.out_ld + (long long)n_blk * BLOCK_N;
   Elem* dst_final = reinterpret_cast<Elem*>(p.out_final) + row * p.out_final_ld + (long long)n_blk * BLOCK_N;
   float coef = (p.out_div != nullptr) ? p.out_scale / __ldg(p.out_div) : p.out_scale;
-  if (p.row_coef != nullptr) coef *= p.row_coef[row];
+  if (p.row_coef != nullptr) coef *= p.row_coef[row];  // row_coef covers the padded rows too
 #pragma unroll 1
   for (int c = 0; c < BLOCK_N / 32; ++c) {
     uint32_t v[32];
-    tmem_ld_32x32b_x32(taddr + c * 32, v);
+    tmem_ld_32x32b_x32(taddr + c * 32, v);  // warp-collective: every lane takes part, even for rows that do not exist
     tmem_ld_wait();
+    const int lim = ncols - c * 32;
     float r[32];
-    if (p.accumulate) {
+    if (!row_ok || lim <= 0) {
+      // nothing of this chunk exists in the output
+    } else if (lim >= 32 && p.out_vector_ok) {
+      // whole chunk inside the output and 32-byte accesses allowed
+      if (p.accumulate) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t o[8];
-        ld_global_256(dst + c * 32 + 8 * i, o);
+        for (int i = 0; i < 4; ++i) {
+          uint32_t o[8];
+          ld_global_256(dst + c * 32 + 8 * i, o);
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          r[8 * i + k] = fmaf(coef, __uint_as_float(v[8 * i + k]), __uint_as_float(o[k]));
+          for (int k = 0; k < 8; ++k)
+            r[8 * i + k] = fmaf(coef, __uint_as_float(v[8 * i + k]), __uint_as_float(o[k]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = coef * __uint_as_float(v[i]);
       }
+      if (p.out_final != nullptr)
+        store_slab_chunk(dst_final + c * 32, r);
+      else
+        store_slab_chunk(dst + c * 32, r);
     } else {
+      // edge of the output, or an unaligned output: element by element
 #pragma unroll
-      for (int i = 0; i < 32; ++i) r[i] = coef * __uint_as_float(v[i]);
+      for (int i = 0; i < 32; ++i) {
+        if (i < lim) {
+          float val = coef * __uint_as_float(v[i]);
+          if (p.accumulate) val += dst[c * 32 + i];
+          if (p.out_final != nullptr)
+            dst_final[c * 32 + i] = cast_elem<Elem>(val);
+          else
+            dst[c * 32 + i] = val;
+        }
+      }
     }
-    if (p.out_final != nullptr)
-      store_slab_chunk(dst_final + c * 32, r);
-    else
-      store_slab_chunk(dst + c * 32, r);
+    __syncwarp();  // the next TMEM load is warp-collective
   }
 }
 

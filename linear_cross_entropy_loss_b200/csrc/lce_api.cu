@@ -97,6 +97,11 @@ int sm_count_or_default() {
 // ------------------------------------------------------------------------------------------------
 inline int elem_size(int dtype) { return dtype == LCE_DTYPE_F32 ? 4 : 2; }
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+inline long long round_up(long long v, long long a) { return (v + a - 1) / a * a; }
+// Tiles are 128 rows x 256 columns; sizes that are not multiples are padded inside the workspace and masked in
+// the kernels (TMA zero-fills what it reads outside x, W).
+inline long long vocab_pad(const lce_problem* p) { return round_up(p->vocab_local, BLOCK_N); }
+inline long long hidden_pad(const lce_problem* p) { return round_up(p->hidden, BLOCK_N); }
 
 int validate_problem(const lce_problem* p) {
   if (p == nullptr) return LCE_ERR_INVALID_ARGUMENT;
@@ -106,9 +111,9 @@ int validate_problem(const lce_problem* p) {
     return LCE_ERR_INVALID_ARGUMENT;
   if (p->world < 1 || p->vocab_offset < 0) return LCE_ERR_INVALID_ARGUMENT;
   if (!(p->logit_scale > 0.f) || !(p->z_regularization >= 0.f)) return LCE_ERR_INVALID_ARGUMENT;
-  if (p->chunk_rows > p->n_rows_total) return LCE_ERR_INVALID_ARGUMENT;
-  if (p->n_rows_total % BLOCK_M != 0 || p->chunk_rows % BLOCK_M != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
-  if (p->hidden % 256 != 0 || p->vocab_local % 256 != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
+  if (p->chunk_rows % BLOCK_M != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
+  // rows of x and W must start on 16-byte boundaries (TMA) and are handled 8 elements at a time
+  if (p->hidden % 8 != 0 || p->vocab_local % 8 != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
   // TMA coordinates and the kernels' tile counters are 32-bit
   if (p->n_rows_total > (1ll << 30) || p->hidden > (1ll << 30) || p->vocab_local > (1ll << 30))
     return LCE_ERR_TOO_LARGE;
@@ -118,8 +123,8 @@ int validate_problem(const lce_problem* p) {
 // K-split of the dx contraction (K = vocab_local): the smallest split whose work units fill the
 // SMs to >= 95 % in whole waves; the partials are reduced in a fixed order afterwards.
 int choose_dx_splits(const lce_problem* p, int sms) {
-  const long long tiles = (p->chunk_rows / BLOCK_M) * (p->hidden / BLOCK_N);
-  const long long kblocks = p->vocab_local * elem_size(p->dtype) / 128;
+  const long long tiles = (p->chunk_rows / BLOCK_M) * (hidden_pad(p) / BLOCK_N);
+  const long long kblocks = vocab_pad(p) * elem_size(p->dtype) / 128;
   int best = 1;
   double best_eff = 0.0;
   for (int s = 1; s <= 16; s *= 2) {
@@ -160,7 +165,7 @@ inline bool row_reference_mode(const lce_problem* p) { return p->dtype != LCE_DT
 
 Workspace layout_workspace(const lce_problem* p, void* base, int sms) {
   Workspace w;
-  const size_t n_tiles = (size_t)(p->vocab_local / BLOCK_N);
+  const size_t n_tiles = (size_t)(vocab_pad(p) / BLOCK_N);
   const size_t rows = (size_t)p->chunk_rows;
   const size_t stat_bytes = align_up(n_tiles * rows * sizeof(float), 256);
   char* b = reinterpret_cast<char*>(base);
@@ -182,9 +187,9 @@ Workspace layout_workspace(const lce_problem* p, void* base, int sms) {
   w.row_coef = reinterpret_cast<float*>(take(rows * sizeof(float)));
   w.dx_splits = choose_dx_splits(p, sms);
   if (p->want_grad) {
-    w.slab = take(rows * (size_t)p->vocab_local * elem_size(p->dtype));
-    w.xs = row_reference_mode(p) ? take(rows * (size_t)p->hidden * elem_size(p->dtype)) : nullptr;
-    w.dx_part = reinterpret_cast<float*>(take((size_t)w.dx_splits * rows * (size_t)p->hidden * sizeof(float)));
+    w.slab = take(rows * (size_t)vocab_pad(p) * elem_size(p->dtype));
+    w.xs = row_reference_mode(p) ? take(rows * (size_t)hidden_pad(p) * elem_size(p->dtype)) : nullptr;
+    w.dx_part = reinterpret_cast<float*>(take((size_t)w.dx_splits * rows * (size_t)hidden_pad(p) * sizeof(float)));
   } else {
     w.slab = nullptr;
     w.xs = nullptr;
@@ -314,8 +319,10 @@ int launch_gemm_dtype(int dtype, const CUtensorMap& ta, const CUtensorMap& tb, c
 // cover a whole chunk or a 128-aligned part of it.
 int check_chunk(const lce_problem* p, int64_t row0, int64_t rows) {
   if (row0 < 0 || rows <= 0 || rows > p->chunk_rows || row0 + rows > p->n_rows_total) return LCE_ERR_INVALID_ARGUMENT;
-  if (row0 % p->chunk_rows + rows > p->chunk_rows) return LCE_ERR_INVALID_ARGUMENT;
-  if (rows % BLOCK_M != 0 || row0 % BLOCK_M != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
+  if (row0 % p->chunk_rows + round_up(rows, BLOCK_M) > p->chunk_rows) return LCE_ERR_INVALID_ARGUMENT;
+  if (row0 % BLOCK_M != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
+  // only the last rows of the whole problem may leave a 128-row tile partly empty
+  if (rows % BLOCK_M != 0 && row0 + rows != p->n_rows_total) return LCE_ERR_UNSUPPORTED_SHAPE;
   return LCE_OK;
 }
 
@@ -341,7 +348,8 @@ const char* lce_status_string(int status) {
     case LCE_OK: return "ok";
     case LCE_ERR_INVALID_ARGUMENT: return "invalid argument";
     case LCE_ERR_UNSUPPORTED_SHAPE:
-      return "unsupported shape (rows % 128, hidden % 256 and vocab % 256 must be 0)";
+      return "unsupported shape (chunk rows % 128, hidden % 8 and vocab % 8 must be 0; calls start on 128-row "
+             "boundaries)";
     case LCE_ERR_MISALIGNED: return "pointer or row stride not 16-byte aligned";
     case LCE_ERR_UNSUPPORTED_DEVICE: return "device is not compute capability 10.x (sm_100a required)";
     case LCE_ERR_CUDA: return "CUDA runtime error";
@@ -390,7 +398,9 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
   const int es = elem_size(p->dtype);
   const long long local0 = row0 % p->chunk_rows;  // first row inside the chunk's slab and statistics
 
-  const bool pair = use_pair_kernel(rows / BLOCK_M, sms);
+  const long long rows_pad = round_up(rows, BLOCK_M);
+  const long long v_pad = vocab_pad(p);
+  const bool pair = use_pair_kernel(rows_pad / BLOCK_M, sms);
   CUtensorMap ta, tb;
   if ((v = make_operand_tmap(&ta, p->dtype, false, x, p->hidden, p->n_rows_total, x_ld, BLOCK_M)) != LCE_OK) return v;
   if ((v = make_operand_tmap(&tb, p->dtype, true, weight, p->vocab_local, p->hidden, w_ld, rows_of_b_tile(pair))) !=
@@ -399,13 +409,15 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
 
   GemmParams gp;
   memset(&gp, 0, sizeof(gp));
-  gp.m_tiles = (int)(rows / BLOCK_M);
-  gp.n_tiles = (int)(p->vocab_local / BLOCK_N);
+  gp.m_tiles = (int)(rows_pad / BLOCK_M);
+  gp.n_tiles = (int)(v_pad / BLOCK_N);
   gp.splits = 1;
-  gp.k_blocks = (int)(p->hidden * es / 128);
+  gp.k_blocks = (int)((p->hidden * es + 127) / 128);
   gp.a_mn0 = (int)row0;
-  gp.slab = w.slab ? reinterpret_cast<char*>(w.slab) + (size_t)local0 * (size_t)p->vocab_local * es : nullptr;
-  gp.slab_ld = p->vocab_local;
+  gp.slab = w.slab ? reinterpret_cast<char*>(w.slab) + (size_t)local0 * (size_t)v_pad * es : nullptr;
+  gp.slab_ld = v_pad;
+  gp.rows_valid = (int)rows;
+  gp.cols_valid = (int)p->vocab_local;
   gp.store_slab = (p->want_grad && w.slab != nullptr) ? 1 : 0;
   gp.tile_max = w.tile_max + local0;
   gp.tile_sum = w.tile_sum + local0;
@@ -497,43 +509,45 @@ int lce_dz_chunk(const lce_problem* p, const void* x, int64_t x_ld, const int64_
   cudaStream_t st = (cudaStream_t)stream;
   const Workspace w = layout_workspace(p, workspace, sms);
   const int es = elem_size(p->dtype);
-  const int n_vtiles = (int)(p->vocab_local / BLOCK_N);
+  const long long v_pad = vocab_pad(p), h_pad = hidden_pad(p);
+  const long long rows_pad = round_up(rows, BLOCK_M);
+  const int n_vtiles = (int)(v_pad / BLOCK_N);
   const long long local0 = row0 % p->chunk_rows;
   const long long* lab = reinterpret_cast<const long long*>(labels) + row0;
-  char* slab = reinterpret_cast<char*>(w.slab) + (size_t)local0 * (size_t)p->vocab_local * es;
+  char* slab = reinterpret_cast<char*>(w.slab) + (size_t)local0 * (size_t)v_pad * es;
   if (row_reference_mode(p)) {
     // per-row factor, scaled copy of the x rows, label entry of the slab: see row_finish_kernel
     const char* xrows = reinterpret_cast<const char*>(x) + (size_t)row0 * (size_t)x_ld * es;
-    char* xs = reinterpret_cast<char*>(w.xs) + (size_t)local0 * (size_t)p->hidden * es;
+    char* xs = reinterpret_cast<char*>(w.xs) + (size_t)local0 * (size_t)h_pad * es;
     if (p->dtype == LCE_DTYPE_BF16)
-      row_finish_kernel<__nv_bfloat16><<<(int)rows, 256, 0, st>>>(
-          reinterpret_cast<const __nv_bfloat16*>(xrows), x_ld, reinterpret_cast<__nv_bfloat16*>(xs), p->hidden,
-          (int)p->hidden, reinterpret_cast<__nv_bfloat16*>(slab), p->vocab_local, w.row_base + local0, w.lse + local0,
-          lab, p->ignore_index, p->vocab_offset, p->vocab_local, p->z_regularization, w.row_coef + local0);
+      row_finish_kernel<__nv_bfloat16><<<(int)rows_pad, 256, 0, st>>>(
+          reinterpret_cast<const __nv_bfloat16*>(xrows), x_ld, reinterpret_cast<__nv_bfloat16*>(xs), h_pad,
+          (int)p->hidden, reinterpret_cast<__nv_bfloat16*>(slab), v_pad, w.row_base + local0, w.lse + local0, lab,
+          (int)rows, p->ignore_index, p->vocab_offset, p->vocab_local, p->z_regularization, w.row_coef + local0);
     else
-      row_finish_kernel<float><<<(int)rows, 256, 0, st>>>(
-          reinterpret_cast<const float*>(xrows), x_ld, reinterpret_cast<float*>(xs), p->hidden, (int)p->hidden,
-          reinterpret_cast<float*>(slab), p->vocab_local, w.row_base + local0, w.lse + local0, lab, p->ignore_index,
-          p->vocab_offset, p->vocab_local, p->z_regularization, w.row_coef + local0);
+      row_finish_kernel<float><<<(int)rows_pad, 256, 0, st>>>(
+          reinterpret_cast<const float*>(xrows), x_ld, reinterpret_cast<float*>(xs), h_pad, (int)p->hidden,
+          reinterpret_cast<float*>(slab), v_pad, w.row_base + local0, w.lse + local0, lab, (int)rows,
+          p->ignore_index, p->vocab_offset, p->vocab_local, p->z_regularization, w.row_coef + local0);
     return check_launch();
   }
-  const long long items = (rows / 8) * n_vtiles;
+  const long long items = (rows_pad / 8) * n_vtiles;
   const int grid = grid_for(items, 1, sms, 16);
   switch (p->dtype) {
     case LCE_DTYPE_F16:
-      dz_transform_kernel<__half><<<grid, 256, 0, st>>>(reinterpret_cast<__half*>(slab), p->vocab_local,
-                                                        w.tile_max + local0, w.lse + local0, lab, (int)rows, n_vtiles,
+      dz_transform_kernel<__half><<<grid, 256, 0, st>>>(reinterpret_cast<__half*>(slab), v_pad, w.tile_max + local0,
+                                                        w.lse + local0, lab, (int)rows_pad, (int)rows, n_vtiles,
                                                         p->chunk_rows, p->ignore_index, p->vocab_offset,
                                                         p->z_regularization);
       break;
     case LCE_DTYPE_BF16:
       dz_transform_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-          reinterpret_cast<__nv_bfloat16*>(slab), p->vocab_local, w.tile_max + local0, w.lse + local0, lab, (int)rows,
-          n_vtiles, p->chunk_rows, p->ignore_index, p->vocab_offset, p->z_regularization);
+          reinterpret_cast<__nv_bfloat16*>(slab), v_pad, w.tile_max + local0, w.lse + local0, lab, (int)rows_pad,
+          (int)rows, n_vtiles, p->chunk_rows, p->ignore_index, p->vocab_offset, p->z_regularization);
       break;
     default:
-      dz_transform_kernel<float><<<grid, 256, 0, st>>>(reinterpret_cast<float*>(slab), p->vocab_local,
-                                                       w.tile_max + local0, w.lse + local0, lab, (int)rows, n_vtiles,
+      dz_transform_kernel<float><<<grid, 256, 0, st>>>(reinterpret_cast<float*>(slab), v_pad, w.tile_max + local0,
+                                                       w.lse + local0, lab, (int)rows_pad, (int)rows, n_vtiles,
                                                        p->chunk_rows, p->ignore_index, p->vocab_offset,
                                                        p->z_regularization);
   }
@@ -557,28 +571,31 @@ int lce_dx_chunk(const lce_problem* p, const void* weight, int64_t w_ld, int64_t
   const long long local0 = row0 % p->chunk_rows;
 
   // partials[s] = dZ * W^T over K-split s of the vocabulary, scaled by logit_scale / n_valid
-  const bool pair = use_pair_kernel(rows / BLOCK_M, sms);
+  const long long v_pad = vocab_pad(p), h_pad = hidden_pad(p);
+  const long long rows_pad = round_up(rows, BLOCK_M);
+  const bool pair = use_pair_kernel(rows_pad / BLOCK_M, sms);
   CUtensorMap ta, tb;
-  if ((v = make_operand_tmap(&ta, p->dtype, false, w.slab, p->vocab_local, p->chunk_rows, p->vocab_local, BLOCK_M)) !=
-      LCE_OK)
-    return v;
+  if ((v = make_operand_tmap(&ta, p->dtype, false, w.slab, v_pad, p->chunk_rows, v_pad, BLOCK_M)) != LCE_OK) return v;
   if ((v = make_operand_tmap(&tb, p->dtype, false, weight, p->vocab_local, p->hidden, w_ld, rows_of_b_tile(pair))) !=
       LCE_OK)
     return v;
-  float* part = w.dx_part + local0 * p->hidden;
+  float* part = w.dx_part + local0 * h_pad;
   GemmParams gp;
   memset(&gp, 0, sizeof(gp));
-  gp.m_tiles = (int)(rows / BLOCK_M);
-  gp.n_tiles = (int)(p->hidden / BLOCK_N);
+  gp.m_tiles = (int)(rows_pad / BLOCK_M);
+  gp.n_tiles = (int)(h_pad / BLOCK_N);
   gp.splits = w.dx_splits;
-  gp.k_blocks = (int)(p->vocab_local * es / 128 / w.dx_splits);
+  gp.k_blocks = (int)(v_pad * es / 128 / w.dx_splits);
   gp.a_mn0 = (int)local0;
   // N-first: the units in flight at one time then cover all H tiles of a few row blocks, so each slab row block is
   // streamed from DRAM once and only the (smaller) weight is re-read per group of row blocks
   gp.n_fastest = (g_gemm_variant.load(std::memory_order_relaxed) & 2) ? 0 : 1;
-  gp.out = part;
-  gp.out_ld = p->hidden;
-  gp.out_split_stride = (long long)p->chunk_rows * p->hidden;
+  gp.out = part;  // padded partial buffer: whole tiles are stored, the reduction below reads what exists
+  gp.out_ld = h_pad;
+  gp.out_split_stride = (long long)p->chunk_rows * h_pad;
+  gp.out_rows = (int)rows_pad;
+  gp.out_cols = (int)h_pad;
+  gp.out_vector_ok = 1;
   gp.accumulate = 0;
   gp.out_scale = p->logit_scale;
   gp.out_div = &w.scalars->n_valid;
@@ -593,19 +610,19 @@ int lce_dx_chunk(const lce_problem* p, const void* weight, int64_t w_ld, int64_t
   // fixed-order sum of the partials -> dx rows
   const long long quads = rows * (p->hidden / 4);
   const int grid = grid_for(quads, 256, sms, 8);
-  const long long ss = (long long)p->chunk_rows * p->hidden;
+  const long long ss = (long long)p->chunk_rows * h_pad;
   char* dx_rows = reinterpret_cast<char*>(dx) + (size_t)row0 * (size_t)dx_ld * elem_size(dx_dtype);
   switch (dx_dtype) {
     case LCE_DTYPE_F16:
-      dx_reduce_kernel<__half><<<grid, 256, 0, st>>>(part, w.dx_splits, ss, (int)rows, (int)p->hidden,
+      dx_reduce_kernel<__half><<<grid, 256, 0, st>>>(part, w.dx_splits, ss, h_pad, (int)rows, (int)p->hidden,
                                                      reinterpret_cast<__half*>(dx_rows), dx_ld);
       break;
     case LCE_DTYPE_BF16:
-      dx_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(part, w.dx_splits, ss, (int)rows, (int)p->hidden,
+      dx_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(part, w.dx_splits, ss, h_pad, (int)rows, (int)p->hidden,
                                                             reinterpret_cast<__nv_bfloat16*>(dx_rows), dx_ld);
       break;
     default:
-      dx_reduce_kernel<float><<<grid, 256, 0, st>>>(part, w.dx_splits, ss, (int)rows, (int)p->hidden,
+      dx_reduce_kernel<float><<<grid, 256, 0, st>>>(part, w.dx_splits, ss, h_pad, (int)rows, (int)p->hidden,
                                                     reinterpret_cast<float*>(dx_rows), dx_ld);
   }
   return check_launch();
@@ -623,10 +640,8 @@ int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0
   const bool need_acc = !(first && dweight_final != nullptr);
   if (need_acc && (!dweight_acc || dw_ld < p->vocab_local)) return LCE_ERR_INVALID_ARGUMENT;
   if (dweight_final && dwf_ld < p->vocab_local) return LCE_ERR_INVALID_ARGUMENT;
-  // the epilogue moves 32-byte sectors
-  if (dweight_acc && ((reinterpret_cast<uintptr_t>(dweight_acc) & 31u) != 0 || (dw_ld & 7) != 0))
-    return LCE_ERR_MISALIGNED;
-  if (dweight_final && ((reinterpret_cast<uintptr_t>(dweight_final) & 31u) != 0 || (dwf_ld & 15) != 0))
+  if (dweight_acc && (reinterpret_cast<uintptr_t>(dweight_acc) & 3u) != 0) return LCE_ERR_MISALIGNED;
+  if (dweight_final && (reinterpret_cast<uintptr_t>(dweight_final) & (uintptr_t)(elem_size(p->dtype) - 1)) != 0)
     return LCE_ERR_MISALIGNED;
   int sms = 0;
   if ((v = ensure_device(&sms)) != LCE_OK) return v;
@@ -636,22 +651,31 @@ int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0
   const long long local0 = row0 % p->chunk_rows;
 
   // dW (+)= x^T * dZ, scaled by logit_scale / n_valid
-  const bool pair = use_pair_kernel(p->hidden / BLOCK_M, sms);
+  const long long v_pad = vocab_pad(p), h_pad = hidden_pad(p);
+  const long long rows_pad = round_up(rows, BLOCK_M);
+  const bool pair = use_pair_kernel(h_pad / BLOCK_M, sms);
   const bool rowref = row_reference_mode(p);
   CUtensorMap ta, tb;
-  // A operand (M = hidden, K = rows): the x rows themselves, or in row-reference mode their scaled copy
-  v = rowref ? make_operand_tmap(&ta, p->dtype, true, w.xs, p->hidden, p->chunk_rows, p->hidden, BLOCK_M)
+  // A operand (M = hidden, K = rows): the x rows themselves, or in row-reference mode their scaled copy. Both maps
+  // describe only what exists; TMA returns zeros for hidden columns / rows beyond it.
+  v = rowref ? make_operand_tmap(&ta, p->dtype, true, w.xs, p->hidden, p->chunk_rows, h_pad, BLOCK_M)
              : make_operand_tmap(&ta, p->dtype, true, x, p->hidden, p->n_rows_total, x_ld, BLOCK_M);
   if (v != LCE_OK) return v;
-  if ((v = make_operand_tmap(&tb, p->dtype, true, w.slab, p->vocab_local, p->chunk_rows, p->vocab_local,
-                             rows_of_b_tile(pair))) != LCE_OK)
+  if ((v = make_operand_tmap(&tb, p->dtype, true, w.slab, v_pad, p->chunk_rows, v_pad, rows_of_b_tile(pair))) != LCE_OK)
     return v;
+  // 32-byte epilogue accesses need 32-byte aligned rows in both outputs; otherwise the epilogue goes element-wise
+  auto rows_aligned32 = [](const void* ptr, long long ld_bytes) {
+    return ptr == nullptr || ((reinterpret_cast<uintptr_t>(ptr) & 31u) == 0 && (ld_bytes & 31) == 0);
+  };
   GemmParams gp;
   memset(&gp, 0, sizeof(gp));
-  gp.m_tiles = (int)(p->hidden / BLOCK_M);
-  gp.n_tiles = (int)(p->vocab_local / BLOCK_N);
+  gp.m_tiles = (int)(h_pad / BLOCK_M);
+  gp.n_tiles = (int)(v_pad / BLOCK_N);
   gp.splits = 1;
-  gp.k_blocks = (int)(rows * es / 128);
+  gp.k_blocks = (int)(rows_pad * es / 128);
+  gp.out_rows = (int)p->hidden;
+  gp.out_cols = (int)p->vocab_local;
+  gp.out_vector_ok = (rows_aligned32(dweight_acc, dw_ld * 4) && rows_aligned32(dweight_final, dwf_ld * es)) ? 1 : 0;
   gp.a_k0 = (int)(rowref ? local0 : row0);
   gp.b_k0 = (int)local0;
   gp.out = dweight_acc;
@@ -818,6 +842,9 @@ int lce_debug_gemm(int32_t dtype, int32_t a_mn_major, int32_t b_mn_major, const 
   gp.out = out;
   gp.out_ld = n;
   gp.out_split_stride = m * n;
+  gp.out_rows = (int)m;
+  gp.out_cols = (int)n;
+  gp.out_vector_ok = ((reinterpret_cast<uintptr_t>(out) & 31u) == 0) ? 1 : 0;
   gp.out_scale = 1.f;
   gp.status = dev_status;
   gp.clock_probe = reinterpret_cast<long long*>(dev_status + 2);
@@ -869,12 +896,12 @@ extern "C" int lce_eval_loss_static(const lce_problem* p_in, const void* x, int6
   p.want_grad = 0;
   p.world = 1;
   p.vocab_offset = 0;
-  p.chunk_rows = p.n_rows_total < BLOCK_M ? p.n_rows_total : BLOCK_M;  // provisional, for the shape checks
+  p.chunk_rows = BLOCK_M;  // provisional, for the shape checks
   int v = validate_problem(&p);
   if (v != LCE_OK) return v;
   const int sms = sm_count_or_default();
   long long best = 0;
-  for (long long rows = BLOCK_M; rows <= p.n_rows_total; rows += BLOCK_M) {
+  for (long long rows = BLOCK_M; rows <= round_up(p.n_rows_total, BLOCK_M); rows += BLOCK_M) {
     p.chunk_rows = rows;
     const size_t need = align_up(layout_workspace(&p, nullptr, sms).total, 256) + (size_t)ROW_PARTS * rows * sizeof(float);
     if (need > (size_t)LCE_STATIC_SCRATCH_BYTES) break;

@@ -199,12 +199,13 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     assert x.dtype == At.dtype, "x and the weight must have the same dtype"
     assert x.dtype in _DTYPE_CODE, f"unsupported dtype {x.dtype}"
     assert y.dtype == torch.int64, "labels must be int64"
-    assert N % 128 == 0, "the number of rows (B*S) must be divisible by 128"
-    assert V % 256 == 0, "the (local) vocabulary size must be divisible by 256"
-    assert H % 256 == 0, "the hidden size must be divisible by 256"
+    assert N >= 1, "x must have at least one row"
+    assert V % 8 == 0, "the (local) vocabulary size must be divisible by 8"
+    assert H % 8 == 0, "the hidden size must be divisible by 8"
     assert logit_scale > 0 and z_regularization >= 0
-    N_group = min(N, int(N_chunk_size))
-    assert N_group % 128 == 0, "N_chunk_size must be divisible by 128"
+    assert int(N_chunk_size) >= 1
+    # rows per chunk as in the reference (ops.py:687), rounded up to the 128-row tile of the kernels
+    N_group = -(-min(N, int(N_chunk_size)) // 128) * 128
 
     world = 1 if shard is None else shard.world
     prob = Problem(
@@ -331,6 +332,7 @@ class LinearXentImplementation(torch.autograd.Function):
         return gx, None, gA, None, None, None, None, None
 
 
+@torch.compiler.disable  # the kernels are reached through ctypes: under torch.compile this call runs eagerly
 def linear_cross_entropy(
     x,
     y,
@@ -359,9 +361,9 @@ class LinearCrossEntropyLoss(torch.nn.Linear):
     ``logit_norm``, ``logit_max``, ``logit_entropy`` and ``z_value``, defined as in the reference's
     ``reference_torch`` (ops.py:9-17).
 
-    Differences from the reference, all of them relaxations: shapes need only N % 128, H % 256 and
-    V % 256 (the reference needs N % 512, H % 256, V % 4096), there is no autotuning on the first call,
-    and gradients are only computed when an input requires them.
+    Differences from the reference, all of them relaxations: any number of rows, H % 8 and V % 8 (the
+    reference needs N % 512, H % 256, V % 4096), there is no autotuning on the first call, and gradients are
+    only computed when an input requires them.
     """
 
     def __init__(
@@ -379,9 +381,9 @@ class LinearCrossEntropyLoss(torch.nn.Linear):
         factory_kwargs = {"device": device, "dtype": dtype}
         torch.nn.Module.__init__(self)  # not nn.Linear.__init__: no bias, transposed weight
 
-        assert in_features % 256 == 0
-        assert out_features % 256 == 0
-        assert N_chunk_size % 128 == 0
+        assert in_features % 8 == 0
+        assert out_features % 8 == 0
+        assert N_chunk_size >= 1
         assert logit_scale > 0
         assert z_regularization >= 0
 
@@ -407,6 +409,7 @@ class LinearCrossEntropyLoss(torch.nn.Linear):
             std = math.sqrt(1 / self.in_features)
             torch.nn.init.trunc_normal_(self.weight, mean=0.0, std=std, a=-3 * std, b=3 * std)
 
+    @torch.compiler.disable  # runs eagerly inside a compiled model (graph break around the ctypes calls)
     def forward(self, x, y):
         loss, z_reg, logit_max, logit_ent, logit_norm = LinearXentImplementation.apply(
             x, y, self.weight, self.ignore_index, self.z_regularization, self.logit_scale, self.N_chunk_size,

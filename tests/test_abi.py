@@ -77,8 +77,8 @@ def test_workspace_size_accounts_for_slab_statistics_and_partials(lib):
 
 @pytest.mark.parametrize("kw,code", [
     (dict(dtype=7), -1), (dict(hidden=0), -1), (dict(logit_scale=0.0), -1), (dict(z_regularization=-1.0), -1),
-    (dict(world=0), -1), (dict(chunk_rows=2048), -1),
-    (dict(hidden=384), -2), (dict(vocab_local=4000), -2), (dict(chunk_rows=192), -2), (dict(n_rows_total=1000), -2),
+    (dict(world=0), -1), (dict(n_rows_total=0), -1),
+    (dict(hidden=100), -2), (dict(vocab_local=4001), -2), (dict(chunk_rows=192), -2),
     (dict(vocab_local=1 << 31), -8),
 ])
 def test_invalid_problems_are_rejected_without_a_device(lib, kw, code):
@@ -104,6 +104,8 @@ def test_chunk_bounds_are_checked(lib):
     assert lib.lce_forward_chunk(ctypes.byref(p), *args, 0, 512, 16, 16, None) == -1    # more rows than a chunk
     assert lib.lce_forward_chunk(ctypes.byref(p), *args, 1024, 256, 16, 16, None) == -1  # past the end
     assert lib.lce_forward_chunk(ctypes.byref(p), *args, 64, 128, 16, 16, None) == -2    # unaligned start
+    assert lib.lce_forward_chunk(ctypes.byref(p), *args, 0, 100, 16, 16, None) == -2     # ragged rows not at the end
+    assert lib.lce_forward_chunk(ctypes.byref(p), *args, 768, 300, 16, 16, None) == -1   # crosses a chunk boundary
 
 
 def test_launch_counter_starts_at_zero_without_a_gpu(lib):

@@ -74,6 +74,20 @@ def test_ragged_last_chunk_and_single_chunk(chunk, N):
     check_against_oracle(x, y, W, torch.bfloat16, ignore=-1, chunk=chunk)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("N,H,V,chunk", [
+    (200, 264, 1000, 128),     # everything ragged; bf16 dW rows are only 16-byte aligned -> element-wise epilogue
+    (1000, 768, 50264, 512),   # GPT-2 vocabulary padded to a multiple of 8, ragged last chunk
+    (72, 64, 1056, 4096),      # fewer rows than one tile, single chunk, aligned rows with a partial last tile
+    (640, 320, 151936 // 8, 256),
+])
+def test_shapes_that_are_not_multiples_of_the_tiles(dtype, N, H, V, chunk):
+    x, y, W = random_problem(N, H, V, torch.bfloat16, seed=N + V)
+    x, W = x.to(dtype), W.to(dtype)            # bf16-representable values: exact TF32 operands too
+    y[-1] = V - 1                              # a label in the last, partial vocabulary tile
+    check_against_oracle(x, y, W, dtype, ignore=-1, zreg=1e-4, scale=0.75, chunk=chunk)
+
+
 def test_labels_on_tile_boundaries_and_repeated_labels():
     x, y, W = random_problem(256, 256, 1024, torch.float16, seed=5, frac=0.0)
     y[:8] = torch.tensor([0, 255, 256, 511, 512, 767, 768, 1023])

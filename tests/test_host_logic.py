@@ -91,15 +91,24 @@ def test_non_contiguous_inputs_are_accepted(fake):
 def test_shape_and_dtype_checks(fake):
     x, y, W = make()
     with pytest.raises(AssertionError):
-        linear_cross_entropy(x[:100], y[:100], W)
+        linear_cross_entropy(x[:, :100], y, W[:100])
     with pytest.raises(AssertionError):
         linear_cross_entropy(x, y, W[:, :100])
     with pytest.raises(AssertionError):
         linear_cross_entropy(x, y.int(), W)
     with pytest.raises(AssertionError):
         linear_cross_entropy(x, y, W.half())
-    with pytest.raises(AssertionError):
-        linear_cross_entropy(x, y, W, N_chunk_size=100)
+
+
+def test_ragged_row_count_and_chunk_size_are_rounded_to_tiles(fake):
+    x, y, W = make(N=300, H=64, V=200)
+    x.requires_grad_(True)
+    out = linear_cross_entropy(x, y, W.requires_grad_(True), ignore_index=-1, N_chunk_size=100)
+    out[0].backward()
+    ref = oracle.forward_backward(x, y, W, -1)
+    assert abs(out[0].item() - ref.loss) < 1e-5
+    np.testing.assert_allclose(x.grad.numpy(), ref.dx, atol=1e-7)
+    assert fake.calls.count("forward_chunk") == 3     # chunks of 128, 128 and 44 rows
 
 
 def test_module_surface_matches_the_reference(fake):
@@ -124,7 +133,7 @@ def test_module_surface_matches_the_reference(fake):
 
 
 def test_module_constructor_asserts():
-    for bad in [dict(in_features=100), dict(out_features=1000), dict(N_chunk_size=100), dict(logit_scale=0.0),
+    for bad in [dict(in_features=100), dict(out_features=1001), dict(N_chunk_size=0), dict(logit_scale=0.0),
                 dict(z_regularization=-1.0)]:
         kw = dict(in_features=256, out_features=512)
         kw.update(bad)
@@ -135,6 +144,27 @@ def test_module_constructor_asserts():
 def test_custom_init_method_is_used():
     m = LinearCrossEntropyLoss(256, 512, init_method=lambda w: torch.nn.init.constant_(w, 0.25))
     assert torch.all(m.weight == 0.25)
+
+
+def test_module_inside_torch_compile_runs_eagerly(fake):
+    class Head(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.proj = torch.nn.Linear(64, 64)
+            self.loss = LinearCrossEntropyLoss(64, 200, ignore_index=-1, N_chunk_size=128)
+
+        def forward(self, h, y):
+            return self.loss(torch.tanh(self.proj(h)), y)
+
+    torch.manual_seed(0)
+    head = Head()
+    h = torch.randn(256, 64)
+    y = torch.randint(0, 200, (256,))
+    eager = head(h, y)
+    compiled = torch.compile(head, backend="eager")(h, y)
+    assert abs(eager.item() - compiled.item()) < 1e-6
+    compiled.backward()
+    assert head.proj.weight.grad is not None and head.loss.weight.grad is not None
 
 
 def test_export_names_of_the_reference_package():

@@ -74,7 +74,7 @@ def test_sizes_beyond_the_fixed_scratch_are_refused():
     rc = lib.lce_eval_loss_static(ctypes.byref(too_wide), x.data_ptr(), 256, x.data_ptr(), 256 * 16384, y.data_ptr(),
                                   out5.data_ptr(), None)
     assert rc == -8 and "maximum" in _native.status_string(rc)
-    bad_shape = _native.Problem(n_rows_total=100, chunk_rows=128, hidden=256, vocab_local=512, vocab_offset=0,
+    bad_shape = _native.Problem(n_rows_total=128, chunk_rows=128, hidden=252, vocab_local=512, vocab_offset=0,
                                 ignore_index=-1, world=1, dtype=1, monitoring=0, want_grad=0, logit_scale=1.0,
                                 z_regularization=0.0)
     assert lib.lce_eval_loss_static(ctypes.byref(bad_shape), x.data_ptr(), 256, x.data_ptr(), 512, y.data_ptr(),
