@@ -15,7 +15,9 @@ from pathlib import Path
 _PKG_DIR = Path(__file__).resolve().parent
 _CSRC = _PKG_DIR / "csrc"
 _INCLUDE = _PKG_DIR.parent / "include"
-LIB_PATH = _PKG_DIR / "liblce_b200.so"
+# LCE_B200_LIB points at an alternative build of the library (A/B measurements); it is used as it is, never rebuilt.
+_OVERRIDE = os.environ.get("LCE_B200_LIB")
+LIB_PATH = Path(_OVERRIDE) if _OVERRIDE else _PKG_DIR / "liblce_b200.so"
 
 LCE_OK = 0
 DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
@@ -57,6 +59,8 @@ def _sources():
 
 
 def needs_build() -> bool:
+    if _OVERRIDE:
+        return False
     if not LIB_PATH.exists():
         return True
     built = LIB_PATH.stat().st_mtime
