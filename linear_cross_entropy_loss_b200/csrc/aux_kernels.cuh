@@ -31,8 +31,16 @@ struct PassScalars {
 //   [0] base b (the reference the sums are relative to), [1] sum_j exp(z - b), [2] target logit (0 if not owned),
 //   [3] sum_j exp(z - b) z, [4] sum_j z^2, [5] max_j z
 constexpr int ROW_PARTS = 6;
-// |row max - reference| beyond which the forward of a chunk is re-run with reference = row max
-constexpr float kRefRange = 60.f;
+// Row-reference mode keeps exp(z - ref_i) in fp32 / bf16: finite row sums need (row max - ref_i) below about
+// 88 - ln(V), and the entries that matter (within ~25 of the row max) need it above about -60. Outside
+// [-kRefBelow, kRefAbove] the forward of the chunk is re-run with ref_i = row max.
+constexpr float kRefAbove = 72.f;
+constexpr float kRefBelow = 60.f;
+// The first forward takes ref_i = (max logit over the first kProbeTiles vocabulary tiles) + kProbeMargin: the
+// probe maximum never exceeds the row maximum, so the margin centres the window on the gap between the two
+// (gaps of -2 .. 130 pass: logits with a standard deviation up to about 45 at V = 131072).
+constexpr int kProbeTiles = 2;
+constexpr float kProbeMargin = 58.f;
 
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ double block_sum_double(double v, double* scratch /*[32]*/) {
@@ -64,7 +72,8 @@ __device__ __forceinline__ float block_max_float(float v, float* scratch /*[32]*
 
 // One block. Counts labels != ignore_index and resets the accumulators of the pass.
 __global__ void begin_kernel(const long long* __restrict__ labels, long long n, long long ignore_index,
-                             PassScalars* sc) {
+                             PassScalars* sc, int* rescue_groups, int n_groups) {
+  for (int g = threadIdx.x; g < n_groups; g += blockDim.x) rescue_groups[g] = 0;
   __shared__ double scratch[32];
   double cnt = 0.0;
   for (long long i = threadIdx.x; i < n; i += blockDim.x) cnt += (labels[i] != ignore_index) ? 1.0 : 0.0;
@@ -142,7 +151,8 @@ row_stats_kernel(const float* __restrict__ tile_max, const float* __restrict__ t
 
 // Row-reference mode: all tiles of a row share the reference ref_i (0, or row_ref[i] in a re-run), so the
 // per-tile sums add up. Same thread layout as row_stats_kernel. Also writes row_ref_out[i] = row max (the
-// reference a re-run would use), row_base_out[i] = ref_i, and raises *rescue when |row max - ref_i| > kRefRange.
+// reference a re-run would use), row_base_out[i] = ref_i, and raises *rescue when row max - ref_i leaves
+// [-kRefBelow, kRefAbove].
 // run_if: when non-null and 0 the kernel does nothing (it belongs to a conditional re-run).
 template <bool kMonitor>
 __global__ void __launch_bounds__(256)
@@ -151,8 +161,11 @@ row_stats_rowref_kernel(const float* __restrict__ tile_max, const float* __restr
                         const float* __restrict__ target_logit, const long long* __restrict__ labels, int rows,
                         int n_tiles, long long stat_ld, long long ignore_index, long long vocab_offset,
                         long long vocab_local, const float* row_ref_in, float* row_ref_out, float* row_base_out,
-                        int* rescue, const int* run_if, float* __restrict__ parts) {
-  if (run_if != nullptr && *run_if == 0) return;
+                        int* rescue, int* rescue_groups, int group_row0, const int* run_if,
+                        float* __restrict__ parts) {
+  // rescue_groups[g]: set when a row of the 256-row group g (rows counted from -group_row0) needs the re-run.
+  // In the re-run itself (run_if given) only the flagged groups were recomputed, so only they are re-read.
+  if (run_if != nullptr && (*run_if == 0 || rescue_groups[(group_row0 + blockIdx.x * 32) >> 8] == 0)) return;
   __shared__ float sm[8][4][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.x * 32 + lane;
@@ -192,15 +205,29 @@ row_stats_rowref_kernel(const float* __restrict__ tile_max, const float* __restr
     parts[5 * stat_ld + r] = m;
     row_base_out[r] = ref;
     row_ref_out[r] = m;
-    if (!(fabsf(m - ref) <= kRefRange)) *rescue = 1;  // also catches NaN / inf
+    if (!(m - ref <= kRefAbove && m - ref >= -kRefBelow)) {  // also catches NaN / inf
+      *rescue = 1;
+      rescue_groups[(group_row0 + r) >> 8] = 1;
+    }
   }
+}
+
+// ref_i = max over the probed tiles of the tile maxima + kProbeMargin (see kProbeTiles).
+__global__ void __launch_bounds__(256)
+probe_ref_kernel(const float* __restrict__ tile_max, long long stat_ld, int tiles, int rows,
+                 float* __restrict__ row_ref) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float m = -INFINITY;
+  for (int t = 0; t < tiles; ++t) m = fmaxf(m, tile_max[(long long)t * stat_ld + r]);
+  row_ref[r] = m + kProbeMargin;
 }
 
 // One block of 1024 threads per chunk. parts_all: [world][ROW_PARTS][stat_ld].
 __global__ void __launch_bounds__(1024)
 combine_kernel(const float* __restrict__ parts_all, int world, const long long* __restrict__ labels, int rows,
                long long stat_ld, long long ignore_index, int monitoring, float* __restrict__ lse_out,
-               PassScalars* sc) {
+               PassScalars* sc, int* rescue_groups, int n_groups) {
   __shared__ double scratch_d[32];
   __shared__ float scratch_f[32];
   double a_nll = 0.0, a_lse2 = 0.0, a_ent = 0.0, a_norm = 0.0;
@@ -240,6 +267,7 @@ combine_kernel(const float* __restrict__ parts_all, int world, const long long* 
     sc->max_logit = fmaxf(sc->max_logit, t_max);
     sc->rescue = 0;  // the chunk's conditional re-run (if any) is behind us
   }
+  for (int g = threadIdx.x; g < n_groups; g += blockDim.x) rescue_groups[g] = 0;
 }
 
 __global__ void finalize_kernel(const PassScalars* sc, double n_rows_total, float z_regularization,

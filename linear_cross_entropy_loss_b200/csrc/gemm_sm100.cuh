@@ -104,6 +104,10 @@ struct GemmParams {
 
   // ---- all kernels: when non-null and *run_if == 0 the kernel returns at once (conditional re-run)
   const int* run_if;
+  // ---- conditional re-run, finer: when non-null, a tile is skipped unless a flag is set for one of its
+  // 256-row groups; group g covers rows [256 g, 256 g + 256) counted from row -run_mask_row0 of this call
+  const int* run_mask;
+  int run_mask_row0;
 
   int* status;                 // device status word (0 = ok)
   long long* clock_probe;      // optional [2]: SM cycles and nanoseconds CTA 0 spent in the kernel (diagnostics)
@@ -422,6 +426,16 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr
   }
 }
 
+// True when the tile of `tile_rows` rows starting at row `row0` of this call takes part in the launch.
+__device__ __forceinline__ bool tile_selected(const GemmParams& p, int row0, int tile_rows) {
+  if (p.run_mask == nullptr) return true;
+  const int first = (p.run_mask_row0 + row0) >> 8;
+  const int last = (p.run_mask_row0 + row0 + tile_rows - 1) >> 8;
+  int any = 0;
+  for (int g = first; g <= last; ++g) any |= p.run_mask[g];
+  return any != 0;
+}
+
 // --------------------------------------------------------------------------------------------------
 // the kernel
 // --------------------------------------------------------------------------------------------------
@@ -494,6 +508,7 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int m_blk = p.n_fastest ? rem / p.n_tiles : rem - n_blk * p.m_tiles;
         const int a_mn = p.a_mn0 + m_blk * BLOCK_M;
         const int b_mn = p.b_mn0 + n_blk * BLOCK_N;
+        if (!tile_selected(p, m_blk * BLOCK_M, BLOCK_M)) continue;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) {
             atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_PRODUCER);
@@ -534,6 +549,11 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
+        if (p.run_mask != nullptr) {  // same tile selection as the producer and the epilogue warps
+          const int rem = unit % tiles_mn;
+          const int m_sel = p.n_fastest ? rem / p.n_tiles : rem % p.m_tiles;
+          if (!tile_selected(p, m_sel * BLOCK_M, BLOCK_M)) continue;
+        }
         if (!mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
           atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_MMA);
           break;
@@ -583,6 +603,7 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int rem = unit - split * tiles_mn;
       const int n_blk = p.n_fastest ? rem % p.n_tiles : rem / p.m_tiles;
       const int m_blk = p.n_fastest ? rem / p.n_tiles : rem - n_blk * p.m_tiles;
+      if (!tile_selected(p, m_blk * BLOCK_M, BLOCK_M)) continue;
       if (!mbar_wait_warp(&sh->acc_full[acc], acc_phase, abort_flag)) {
         if (lane == 0) atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_EPILOGUE);
         break;
@@ -731,6 +752,7 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const int m_blk = p.n_fastest ? rem / p.n_tiles : rem - n_blk * p.m_tiles;
         const int a_mn = p.a_mn0 + m_blk * PAIR_M + int(rank) * BLOCK_M;
         const int b_mn = p.b_mn0 + n_blk * BLOCK_N + int(rank) * HALF_N;
+        if (!tile_selected(p, m_blk * PAIR_M, PAIR_M)) continue;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) {
             atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_PRODUCER);
@@ -772,6 +794,11 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int unit = cluster_id; ok && unit < units; unit += n_clusters) {
+        if (p.run_mask != nullptr) {  // same tile selection as the producers and the epilogue warps
+          const int rem = unit % tiles_mn;
+          const int m_sel = p.n_fastest ? rem / p.n_tiles : rem % p.m_tiles;
+          if (!tile_selected(p, m_sel * PAIR_M, PAIR_M)) continue;
+        }
         if (!mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
           atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_MMA);
           break;
@@ -826,6 +853,7 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const int n_blk = p.n_fastest ? rem % p.n_tiles : rem / p.m_tiles;
       const int m_blk = p.n_fastest ? rem / p.n_tiles : rem - n_blk * p.m_tiles;
       const int m_blk128 = m_blk * 2 + int(rank);  // this CTA's 128-row block
+      if (!tile_selected(p, m_blk * PAIR_M, PAIR_M)) continue;
       if (!mbar_wait_warp(&sh->acc_full[acc], acc_phase, abort_flag)) {
         if (lane == 0) atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_EPILOGUE);
         break;

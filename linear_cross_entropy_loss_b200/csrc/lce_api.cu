@@ -152,6 +152,7 @@ struct Workspace {
   float* row_ref;   // row-reference mode: row max of the first forward = reference of a conditional re-run
   float* row_base;  // row-reference mode: the reference the row's slab and sums were computed with
   float* row_coef;  // row-reference mode: exp(base - lse) (1 + 2 z_reg lse), 0 for ignored rows
+  int* rescue_groups;  // row-reference mode: one flag per 256 rows of the chunk: forward must be re-run for them
   void* slab;
   void* xs;         // row-reference mode: row_coef[i] * x[i, :] for the rows of the chunk
   float* dx_part;
@@ -185,6 +186,7 @@ Workspace layout_workspace(const lce_problem* p, void* base, int sms) {
   w.row_ref = reinterpret_cast<float*>(take(rows * sizeof(float)));
   w.row_base = reinterpret_cast<float*>(take(rows * sizeof(float)));
   w.row_coef = reinterpret_cast<float*>(take(rows * sizeof(float)));
+  w.rescue_groups = reinterpret_cast<int*>(take((rows / 256 + 2) * sizeof(int)));
   w.dx_splits = choose_dx_splits(p, sms);
   if (p->want_grad) {
     w.slab = take(rows * (size_t)vocab_pad(p) * elem_size(p->dtype));
@@ -379,7 +381,7 @@ int lce_begin(const lce_problem* p, const int64_t* labels, void* workspace, void
   const Workspace w = layout_workspace(p, workspace, sms);
   begin_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(reinterpret_cast<const long long*>(labels),
                                                      (long long)p->n_rows_total, (long long)p->ignore_index,
-                                                     w.scalars);
+                                                     w.scalars, w.rescue_groups, (int)(p->chunk_rows / 256 + 2));
   return check_launch();
 }
 
@@ -456,26 +458,40 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
     return check_launch();
   }
 
-  // Row-reference mode: forward with reference 0, then -- only if some row's max logit lies outside
-  // +-60 of it, which the statistics kernel reports through the device flag `rescue` -- the same two
-  // kernels again with reference = row max. The second pair returns at once when the flag is clear.
+  // Row-reference mode. A probe -- the forward kernel over the first two vocabulary tiles only, statistics
+  // without slab -- gives each row a reference near its maximum (probe_ref_kernel). Then the forward proper;
+  // then, only if some row's max logit turns out to lie outside the window around its reference (the
+  // statistics kernel reports it through the device flag `rescue`), the same two kernels again with
+  // reference = row max. That second pair returns at once when the flag is clear.
   int* rescue = &w.scalars->rescue;
+  const bool probe = gp.n_tiles > 2 * kProbeTiles;  // tiny vocabularies: reference 0, the re-run covers the rest
+  if (probe) {
+    GemmParams pp = gp;
+    pp.n_tiles = kProbeTiles;
+    pp.store_slab = 0;
+    if ((v = launch_gemm_dtype<false, true, EPI_FWD, false>(p->dtype, ta, tb, pp, sms, st, pair)) != LCE_OK) return v;
+    probe_ref_kernel<<<(int)((rows + 255) / 256), 256, 0, st>>>(gp.tile_max, p->chunk_rows, kProbeTiles, (int)rows,
+                                                               w.row_ref + local0);
+    if ((v = check_launch()) != LCE_OK) return v;
+  }
   for (int pass = 0; pass < 2; ++pass) {
     const int* run_if = pass == 0 ? nullptr : rescue;
-    const float* ref_in = pass == 0 ? nullptr : w.row_ref + local0;
+    const float* ref_in = (pass == 0 && !probe) ? nullptr : w.row_ref + local0;
     gp.row_ref = ref_in;
     gp.run_if = run_if;
+    gp.run_mask = pass == 0 ? nullptr : w.rescue_groups;  // the re-run only touches the flagged 256-row groups
+    gp.run_mask_row0 = (int)local0;
     if ((v = (pass == 0 ? run_forward() : launch_forward())) != LCE_OK) return v;
     if (p->monitoring)
       row_stats_rowref_kernel<true><<<blocks, 256, 0, st>>>(
           gp.tile_max, gp.tile_sum, gp.tile_ez, gp.tile_sq, gp.target_logit, lab, (int)rows, gp.n_tiles,
           p->chunk_rows, p->ignore_index, p->vocab_offset, p->vocab_local, ref_in, w.row_ref + local0,
-          w.row_base + local0, rescue, run_if, parts);
+          w.row_base + local0, rescue, w.rescue_groups, (int)local0, run_if, parts);
     else
       row_stats_rowref_kernel<false><<<blocks, 256, 0, st>>>(
           gp.tile_max, gp.tile_sum, gp.tile_ez, gp.tile_sq, gp.target_logit, lab, (int)rows, gp.n_tiles,
           p->chunk_rows, p->ignore_index, p->vocab_offset, p->vocab_local, ref_in, w.row_ref + local0,
-          w.row_base + local0, rescue, run_if, parts);
+          w.row_base + local0, rescue, w.rescue_groups, (int)local0, run_if, parts);
     if ((v = check_launch()) != LCE_OK) return v;
   }
   return LCE_OK;
@@ -494,7 +510,7 @@ int lce_combine_chunk(const lce_problem* p, const float* row_parts_all, const in
   combine_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(row_parts_all + local0, p->world,
                                                        reinterpret_cast<const long long*>(labels) + row0, (int)rows,
                                                        p->chunk_rows, p->ignore_index, p->monitoring, w.lse + local0,
-                                                       w.scalars);
+                                                       w.scalars, w.rescue_groups, (int)(p->chunk_rows / 256 + 2));
   return check_launch();
 }
 

@@ -132,6 +132,31 @@ def test_conditional_rerun_when_logits_leave_the_reference_range(dtype):
     check_against_oracle(x, y, W, dtype, ignore=-1, scale=32.0, zreg=1e-4, chunk=256)
 
 
+def test_wide_logits_with_probe_reference_and_outlier_column():
+    # V > 1024: the first forward takes its per-row reference from a probe of the first 512 columns. Logits of
+    # spread ~40 stay inside the window; a column far above everything the probe saw forces the re-run.
+    x, y, W = random_problem(256, 256, 4096, torch.bfloat16, seed=23)
+    check_against_oracle(x, y, W, torch.bfloat16, ignore=-1, scale=40.0, chunk=128)
+    x2, W2 = x.clone(), W.clone()
+    x2[:128, 0] = 8.0
+    W2[0, 3000] = 4.0                     # rows 0..127 get a logit near 8 * 4 * 8 = 256 in column 3000
+    got, dxn, dWn, ref = check_against_oracle(x2, y, W2, torch.bfloat16, ignore=-1, scale=8.0, chunk=128)
+    assert ref.logit_max > 200
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rerun_touches_only_the_row_groups_that_need_it(dtype):
+    # 1024-row chunks = four 256-row groups; only rows 300..309 (group 1) and 1900 (second chunk, group 3) carry
+    # a logit far above what the probe of the first 512 columns sees
+    x, y, W = random_problem(2048, 256, 4096, torch.bfloat16, seed=24)
+    x[300:310, 1] = 16.0
+    x[1900, 1] = 16.0
+    W[1, 2500] = 8.0
+    x, W = x.to(dtype), W.to(dtype)
+    got, dxn, dWn, ref = check_against_oracle(x, y, W, dtype, ignore=-1, scale=2.0, zreg=1e-4, chunk=1024)
+    assert ref.logit_max > 200
+
+
 def test_conditional_rerun_on_the_underflow_side():
     g = torch.Generator().manual_seed(22)
     x = (torch.rand(256, 256, generator=g) + 0.5).bfloat16()
