@@ -34,8 +34,8 @@ METRIC = "fwd+bwd TFLOP/s (6NHV/t)"
 PUBLISHED_BF16_DEFAULT_TFLOPS = 86.75
 # fallback roofline denominators when the measured-peaks file is absent (earlier measurement on this pool)
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of each contraction kernel, from the ncu
-# capture of the quarter-size case (V=32768) summarised in profiles/lce_gemm_pair_kernel__profile_small_bf16.md:
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of each contraction kernel, from an ncu
+# capture of the quarter-size case (N=4096, H=2048, V=32768, bf16; summary kept under profiles/):
 # forward 381.9 MB, dx 931.7 MB, dW 406.5 MB. Forward and dx traffic grow in proportion to V; the figures are scaled
 # by V_local / 32768 at run time (only for N_chunk_size=4096, H=2048, which the capture used). dW is not scaled: from
 # the second chunk on it also reads and rewrites the fp32 accumulator, which the one-chunk capture does not contain.

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the kernels use:
-// mbarrier, TMA tiled loads/stores (cp.async.bulk.tensor), tcgen05 (TMEM allocation,
+// mbarrier, TMA tiled loads (cp.async.bulk.tensor), tcgen05 (TMEM allocation,
 // UMMA issue, commit, TMEM loads) and the proxy / thread-sync fences that go with them.
 //
 // Every wait in this file is bounded: a wait that runs past its limit raises an abort
@@ -134,34 +134,6 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
-}
-
-// shared -> global, 2-D tile (bulk async group completion).
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void* smem_src, int c0, int c1) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
-               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
-               : "memory");
-}
-
-// shared -> global, 2-D tile, element-wise add into global memory (f32).
-__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tmap, const void* smem_src, int c0, int c1) {
-  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                   tmap),
-               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
-               : "memory");
-}
-
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-
-// Wait until at most N of this thread's bulk groups still READ shared memory.
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-// Wait until at most N of this thread's bulk groups are still in flight at all.
-template <int N>
-__device__ __forceinline__ void tma_store_wait_all() {
-  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------

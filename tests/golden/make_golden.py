@@ -45,7 +45,9 @@ def make_inputs(seed, N, H, V, ignore_index, frac_ignored):
 
 
 def main():
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path of the reference checkout>")
+    ref_root = Path(sys.argv[1])
     reference_torch = load_reference(ref_root)
     torch.set_num_threads(1)  # fixed summation order
     out = {}
