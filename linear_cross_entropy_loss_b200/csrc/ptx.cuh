@@ -273,6 +273,15 @@ __device__ __forceinline__ void umma_pair_tf32(uint32_t d_tmem, uint64_t adesc, 
 }
 // Arrive on the mbarrier at `bar_cluster_addr` (own or peer CTA) once every tcgen05 operation this
 // thread issued so far -- pair-wide MMAs included -- has completed.
+// Same, arriving on the barrier at this CTA-local offset in both CTAs of the pair with one instruction.
+__device__ __forceinline__ void umma_pair_commit_both(uint32_t bar_local_addr) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          bar_local_addr),
+      "h"(mask)
+      : "memory");
+}
 __device__ __forceinline__ void umma_pair_commit(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                : "memory");
