@@ -137,6 +137,45 @@ int lce_backward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const 
                        int64_t dx_ld, int32_t dx_dtype, float* dweight_acc, int64_t dw_ld, int32_t first,
                        void* dweight_final, int64_t dwf_ld, void* stream);
 
+/* ---- dx exchange between the ranks of a vocabulary-sharded run, over peer-mapped memory -------------------
+ * No counterpart in the reference (it has no multi-GPU path). These three calls replace lce_dx_chunk plus the
+ * all-reduce of the chunk's dx rows that a sharded caller would otherwise issue: the dx contraction itself
+ * stores its fp32 output tiles into the memory of the rank that owns the rows (rank o owns chunk rows
+ * [o * chunk_rows / world, (o + 1) * chunk_rows / world)), the owner sums all ranks' tiles in a fixed order,
+ * rounds once and stores the finished rows into every rank's staging area, from where they are copied into dx.
+ * Only stores and 32-bit flags cross the links. dx comes out bitwise identical on all ranks.
+ *
+ * lce_peer_table: world / rank of the caller and, for every rank, the address AS SEEN FROM THE CALLING GPU of
+ * that rank's exchange buffer (base[rank] is the caller's own). Each buffer holds lce_peer_bytes() bytes, is
+ * 256-byte aligned, must be zero before its first use and is owned by the caller (the library allocates
+ * nothing); all ranks must use the same problem, dx_dtype and sequence of epochs.
+ * epoch: a counter the caller increases by one for every lce_dx_chunk_peer call on this set of buffers
+ * (starting at 1, same value on all ranks); it selects one of two buffer halves and is the value the flags
+ * are compared against.
+ * Requires chunk_rows % (128 * world) == 0 (LCE_ERR_UNSUPPORTED_SHAPE otherwise) and world <= LCE_MAX_PEERS.
+ * Waits on other ranks are bounded by wait_ms (<= 0: 10 s); when one runs out the device status word is set,
+ * nothing is copied and the loss of the pass becomes NaN.
+ *
+ * lce_dx_chunk_peer   contraction + scatter into the owners' buffers, then flag A. Stream-ordered after
+ *                     lce_dz_chunk like lce_dx_chunk.
+ * lce_dx_reduce_peer  waits for flag A of all ranks; sums and broadcasts the rows this rank owns; flag B.
+ * lce_dx_finish_peer  waits for flag B of all ranks; copies the chunk's rows from the staging area into dx.
+ * The last two may run on another stream than the first (ordered after it by an event); at most two epochs
+ * may be in flight: lce_dx_chunk_peer(epoch e) must be ordered after lce_dx_finish_peer(epoch e - 2). */
+#define LCE_MAX_PEERS 8
+typedef struct lce_peer_table {
+  int32_t world;
+  int32_t rank;
+  void* base[LCE_MAX_PEERS];
+} lce_peer_table;
+int lce_peer_bytes(const lce_problem* p, int32_t dx_dtype, size_t* bytes);
+int lce_dx_chunk_peer(const lce_problem* p, const void* weight, int64_t w_ld, int64_t row0, int64_t rows,
+                      void* workspace, const lce_peer_table* peers, int32_t dx_dtype, uint32_t epoch, void* stream);
+int lce_dx_reduce_peer(const lce_problem* p, int64_t row0, int64_t rows, void* workspace, const lce_peer_table* peers,
+                       int32_t dx_dtype, uint32_t epoch, int32_t wait_ms, void* stream);
+int lce_dx_finish_peer(const lce_problem* p, int64_t row0, int64_t rows, void* workspace, const lce_peer_table* peers,
+                       uint32_t epoch, void* dx, int64_t dx_ld, int32_t dx_dtype, int32_t wait_ms, void* stream);
+
 /* out5: float[5] = loss, z_value, logit_max, logit_entropy, logit_norm (the reference's return
  * tuple, ops.py:802). The last three are only meaningful with monitoring. If any kernel of the pass
  * reported a device-side error the loss is NaN. */

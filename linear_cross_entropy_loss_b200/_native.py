@@ -98,6 +98,16 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64
 _i32 = ctypes.c_int32
+_u32 = ctypes.c_uint32
+
+MAX_PEERS = 8
+
+
+class PeerTable(ctypes.Structure):
+    """Mirror of ``lce_peer_table``: every rank's exchange buffer as addressed from this GPU."""
+
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("base", ctypes.c_void_p * MAX_PEERS)]
+
 
 # name -> (restype, argtypes); kept in one table so that a test can check it against the header.
 SIGNATURES = {
@@ -110,6 +120,14 @@ SIGNATURES = {
     "lce_combine_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _vp, _i64, _i64, _vp, _vp]),
     "lce_dz_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _i64, _vp, _vp]),
     "lce_dx_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _vp]),
+    "lce_peer_bytes": (ctypes.c_int, [ctypes.POINTER(Problem), _i32, ctypes.POINTER(ctypes.c_size_t)]),
+    "lce_dx_chunk_peer": (
+        ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _i64, _i64, _vp, ctypes.POINTER(PeerTable), _i32, _u32, _vp]),
+    "lce_dx_reduce_peer": (
+        ctypes.c_int, [ctypes.POINTER(Problem), _i64, _i64, _vp, ctypes.POINTER(PeerTable), _i32, _u32, _i32, _vp]),
+    "lce_dx_finish_peer": (
+        ctypes.c_int,
+        [ctypes.POINTER(Problem), _i64, _i64, _vp, ctypes.POINTER(PeerTable), _u32, _vp, _i64, _i32, _i32, _vp]),
     "lce_dw_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _vp, _i64, _vp]),
     "lce_backward_chunk": (
         ctypes.c_int,

@@ -111,6 +111,13 @@ struct GemmParams {
 
   int* status;                 // device status word (0 = ok)
   long long* clock_probe;      // optional [2]: SM cycles and nanoseconds CTA 0 spent in the kernel (diagnostics)
+  // EPI_F32 scatter mode (peer_rows_own > 0): the output rows are spread over the receive buffers of the ranks
+  // that own them -- rank o owns chunk rows [o * peer_rows_own, (o + 1) * peer_rows_own) -- and split s of
+  // this launch goes to slot peer_slot0 + s of the owner's buffer [slots][peer_rows_own][out_ld] at peer_out[o]
+  float* peer_out[8];
+  int peer_rows_own;           // multiple of BLOCK_M, so that a tile has one owner; 0 = plain output
+  int peer_row0;               // chunk-local index of output row 0 of this launch
+  int peer_slot0;
 };
 
 // --------------------------------------------------------------------------------------------------
@@ -376,7 +383,16 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr
   const long long row = (long long)m_blk * BLOCK_M + row_in_tile;
   const bool row_ok = row < p.out_rows;
   const int ncols = min(BLOCK_N, p.out_cols - n_blk * BLOCK_N);  // columns of this tile that exist
-  float* dst = p.out + (long long)split * p.out_split_stride + row * p.out_ld + (long long)n_blk * BLOCK_N;
+  float* dst;
+  if (p.peer_rows_own > 0) {
+    const int chunk_row = p.peer_row0 + int(row);
+    const int owner = min(chunk_row / p.peer_rows_own, 7);
+    dst = p.peer_out[owner] +
+          ((long long)(p.peer_slot0 + split) * p.peer_rows_own + (chunk_row - owner * p.peer_rows_own)) * p.out_ld +
+          (long long)n_blk * BLOCK_N;
+  } else {
+    dst = p.out + (long long)split * p.out_split_stride + row * p.out_ld + (long long)n_blk * BLOCK_N;
+  }
   Elem* dst_final = reinterpret_cast<Elem*>(p.out_final) + row * p.out_final_ld + (long long)n_blk * BLOCK_N;
   float coef = (p.out_div != nullptr) ? p.out_scale / __ldg(p.out_div) : p.out_scale;
   if (p.row_coef != nullptr) coef *= p.row_coef[row];  // row_coef covers the padded rows too

@@ -4,7 +4,9 @@
 
 #include "aux_kernels.cuh"
 #include "gemm_sm100.cuh"
+#include "peer_exchange.cuh"
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstring>
@@ -570,6 +572,101 @@ int lce_dz_chunk(const lce_problem* p, const void* x, int64_t x_ld, const int64_
   return check_launch();
 }
 
+}  // extern "C"
+
+namespace {
+
+// Where the dx contraction sends its output tiles when the partials are exchanged between ranks.
+struct PeerScatter {
+  PeerBases bases;
+  PeerLayout layout;
+  int world, rank, buf;
+};
+
+PeerLayout layout_peer(const lce_problem* p, int dx_dtype, int splits) {
+  PeerLayout l;
+  l.slots = p->world * splits;
+  l.rows_own = (int)(p->chunk_rows / p->world);
+  l.recv_bytes = round_up((long long)l.slots * l.rows_own * hidden_pad(p) * (long long)sizeof(float), 1024);
+  l.stage_bytes = round_up(p->chunk_rows * p->hidden * (long long)elem_size(dx_dtype), 1024);
+  l.total = kPeerFlagBytes + 2 * l.recv_bytes + 2 * l.stage_bytes;
+  return l;
+}
+
+int check_peers(const lce_problem* p, const lce_peer_table* peers, int dx_dtype) {
+  if (!peers) return LCE_ERR_INVALID_ARGUMENT;
+  if (dx_dtype != LCE_DTYPE_F16 && dx_dtype != LCE_DTYPE_BF16 && dx_dtype != LCE_DTYPE_F32)
+    return LCE_ERR_INVALID_ARGUMENT;
+  if (peers->world != p->world || peers->world < 1 || peers->world > kMaxPeers) return LCE_ERR_INVALID_ARGUMENT;
+  if (peers->rank < 0 || peers->rank >= peers->world) return LCE_ERR_INVALID_ARGUMENT;
+  if (p->chunk_rows % ((long long)BLOCK_M * peers->world) != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
+  for (int g = 0; g < peers->world; ++g) {
+    if (!peers->base[g]) return LCE_ERR_INVALID_ARGUMENT;
+    if ((reinterpret_cast<uintptr_t>(peers->base[g]) & 255u) != 0) return LCE_ERR_MISALIGNED;
+  }
+  return LCE_OK;
+}
+
+PeerBases bases_of(const lce_peer_table* peers) {
+  PeerBases b;
+  for (int g = 0; g < kMaxPeers; ++g)
+    b.base[g] = g < peers->world ? reinterpret_cast<unsigned char*>(peers->base[g]) : nullptr;
+  return b;
+}
+
+// partials[s] = dZ * W^T over K-split s of the vocabulary, scaled by logit_scale / n_valid: into the workspace
+// (scatter == nullptr) or into the owners' receive buffers.
+int launch_dx_gemm(const lce_problem* p, const void* weight, int64_t w_ld, int64_t row0, int64_t rows,
+                   const Workspace& w, int sms, cudaStream_t st, const PeerScatter* scatter) {
+  const int es = elem_size(p->dtype);
+  const long long local0 = row0 % p->chunk_rows;
+  const long long v_pad = vocab_pad(p), h_pad = hidden_pad(p);
+  const long long rows_pad = round_up(rows, BLOCK_M);
+  const bool pair = use_pair_kernel(rows_pad / BLOCK_M, sms);
+  CUtensorMap ta, tb;
+  int v;
+  if ((v = make_operand_tmap(&ta, p->dtype, false, w.slab, v_pad, p->chunk_rows, v_pad, BLOCK_M)) != LCE_OK) return v;
+  if ((v = make_operand_tmap(&tb, p->dtype, false, weight, p->vocab_local, p->hidden, w_ld, rows_of_b_tile(pair))) !=
+      LCE_OK)
+    return v;
+  GemmParams gp;
+  memset(&gp, 0, sizeof(gp));
+  gp.m_tiles = (int)(rows_pad / BLOCK_M);
+  gp.n_tiles = (int)(h_pad / BLOCK_N);
+  gp.splits = w.dx_splits;
+  gp.k_blocks = (int)(v_pad * es / 128 / w.dx_splits);
+  gp.a_mn0 = (int)local0;
+  // N-first: the units in flight at one time then cover all H tiles of a few row blocks, so each slab row block is
+  // streamed from DRAM once and only the (smaller) weight is re-read per group of row blocks
+  gp.n_fastest = (g_gemm_variant.load(std::memory_order_relaxed) & 2) ? 0 : 1;
+  gp.out = w.dx_part + local0 * h_pad;  // padded partial buffer: whole tiles are stored, the reduction reads what exists
+  gp.out_ld = h_pad;
+  gp.out_split_stride = (long long)p->chunk_rows * h_pad;
+  gp.out_rows = (int)rows_pad;
+  gp.out_cols = (int)h_pad;
+  gp.out_vector_ok = 1;
+  gp.accumulate = 0;
+  gp.out_scale = p->logit_scale;
+  gp.out_div = &w.scalars->n_valid;
+  gp.row_coef = row_reference_mode(p) ? w.row_coef + local0 : nullptr;
+  gp.status = &w.scalars->status;
+  if (scatter != nullptr) {
+    for (int g = 0; g < scatter->world; ++g)
+      gp.peer_out[g] = reinterpret_cast<float*>(scatter->bases.base[g] + scatter->layout.recv_off(scatter->buf));
+    gp.peer_rows_own = scatter->layout.rows_own;
+    gp.peer_row0 = (int)local0;
+    gp.peer_slot0 = scatter->rank * w.dx_splits;
+  }
+  ProfScope prof(PROF_DX, st);
+  return launch_gemm_dtype<false, false, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st, pair);
+}
+
+long long peer_wait_limit_ns(int32_t wait_ms) { return (long long)(wait_ms > 0 ? wait_ms : 10000) * 1000000LL; }
+
+}  // namespace
+
+extern "C" {
+
 int lce_dx_chunk(const lce_problem* p, const void* weight, int64_t w_ld, int64_t row0, int64_t rows, void* workspace,
                  void* dx, int64_t dx_ld, int32_t dx_dtype, void* stream) {
   int v = validate_problem(p);
@@ -583,47 +680,12 @@ int lce_dx_chunk(const lce_problem* p, const void* weight, int64_t w_ld, int64_t
   if ((v = ensure_device(&sms)) != LCE_OK) return v;
   cudaStream_t st = (cudaStream_t)stream;
   const Workspace w = layout_workspace(p, workspace, sms);
-  const int es = elem_size(p->dtype);
   const long long local0 = row0 % p->chunk_rows;
-
-  // partials[s] = dZ * W^T over K-split s of the vocabulary, scaled by logit_scale / n_valid
-  const long long v_pad = vocab_pad(p), h_pad = hidden_pad(p);
-  const long long rows_pad = round_up(rows, BLOCK_M);
-  const bool pair = use_pair_kernel(rows_pad / BLOCK_M, sms);
-  CUtensorMap ta, tb;
-  if ((v = make_operand_tmap(&ta, p->dtype, false, w.slab, v_pad, p->chunk_rows, v_pad, BLOCK_M)) != LCE_OK) return v;
-  if ((v = make_operand_tmap(&tb, p->dtype, false, weight, p->vocab_local, p->hidden, w_ld, rows_of_b_tile(pair))) !=
-      LCE_OK)
-    return v;
-  float* part = w.dx_part + local0 * h_pad;
-  GemmParams gp;
-  memset(&gp, 0, sizeof(gp));
-  gp.m_tiles = (int)(rows_pad / BLOCK_M);
-  gp.n_tiles = (int)(h_pad / BLOCK_N);
-  gp.splits = w.dx_splits;
-  gp.k_blocks = (int)(v_pad * es / 128 / w.dx_splits);
-  gp.a_mn0 = (int)local0;
-  // N-first: the units in flight at one time then cover all H tiles of a few row blocks, so each slab row block is
-  // streamed from DRAM once and only the (smaller) weight is re-read per group of row blocks
-  gp.n_fastest = (g_gemm_variant.load(std::memory_order_relaxed) & 2) ? 0 : 1;
-  gp.out = part;  // padded partial buffer: whole tiles are stored, the reduction below reads what exists
-  gp.out_ld = h_pad;
-  gp.out_split_stride = (long long)p->chunk_rows * h_pad;
-  gp.out_rows = (int)rows_pad;
-  gp.out_cols = (int)h_pad;
-  gp.out_vector_ok = 1;
-  gp.accumulate = 0;
-  gp.out_scale = p->logit_scale;
-  gp.out_div = &w.scalars->n_valid;
-  gp.row_coef = row_reference_mode(p) ? w.row_coef + local0 : nullptr;
-  gp.status = &w.scalars->status;
-  {
-    ProfScope prof(PROF_DX, st);
-    v = launch_gemm_dtype<false, false, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st, pair);
-  }
-  if (v != LCE_OK) return v;
+  const long long h_pad = hidden_pad(p);
+  if ((v = launch_dx_gemm(p, weight, w_ld, row0, rows, w, sms, st, nullptr)) != LCE_OK) return v;
 
   // fixed-order sum of the partials -> dx rows
+  const float* part = w.dx_part + local0 * h_pad;
   const long long quads = rows * (p->hidden / 4);
   const int grid = grid_for(quads, 256, sms, 8);
   const long long ss = (long long)p->chunk_rows * h_pad;
@@ -640,6 +702,137 @@ int lce_dx_chunk(const lce_problem* p, const void* weight, int64_t w_ld, int64_t
     default:
       dx_reduce_kernel<float><<<grid, 256, 0, st>>>(part, w.dx_splits, ss, h_pad, (int)rows, (int)p->hidden,
                                                     reinterpret_cast<float*>(dx_rows), dx_ld);
+  }
+  return check_launch();
+}
+
+int lce_peer_bytes(const lce_problem* p, int32_t dx_dtype, size_t* bytes) {
+  int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if (!bytes) return LCE_ERR_INVALID_ARGUMENT;
+  if (dx_dtype != LCE_DTYPE_F16 && dx_dtype != LCE_DTYPE_BF16 && dx_dtype != LCE_DTYPE_F32)
+    return LCE_ERR_INVALID_ARGUMENT;
+  if (p->world < 1 || p->world > kMaxPeers) return LCE_ERR_INVALID_ARGUMENT;
+  if (p->chunk_rows % ((long long)BLOCK_M * p->world) != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
+  int sms = 0;
+  if ((v = ensure_device(&sms)) != LCE_OK) return v;
+  *bytes = layout_peer(p, dx_dtype, choose_dx_splits(p, sms)).total;
+  return LCE_OK;
+}
+
+int lce_dx_chunk_peer(const lce_problem* p, const void* weight, int64_t w_ld, int64_t row0, int64_t rows,
+                      void* workspace, const lce_peer_table* peers, int32_t dx_dtype, uint32_t epoch, void* stream) {
+  int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if ((v = check_chunk(p, row0, rows)) != LCE_OK) return v;
+  if (!p->want_grad || !weight || !workspace) return LCE_ERR_INVALID_ARGUMENT;
+  if (w_ld < p->vocab_local) return LCE_ERR_INVALID_ARGUMENT;
+  if ((v = check_peers(p, peers, dx_dtype)) != LCE_OK) return v;
+  int sms = 0;
+  if ((v = ensure_device(&sms)) != LCE_OK) return v;
+  cudaStream_t st = (cudaStream_t)stream;
+  const Workspace w = layout_workspace(p, workspace, sms);
+  PeerScatter sc;
+  sc.bases = bases_of(peers);
+  sc.layout = layout_peer(p, dx_dtype, w.dx_splits);
+  sc.world = peers->world;
+  sc.rank = peers->rank;
+  sc.buf = (int)(epoch & 1u);
+  if ((v = launch_dx_gemm(p, weight, w_ld, row0, rows, w, sms, st, &sc)) != LCE_OK) return v;
+  peer_signal_kernel<<<1, 32, 0, st>>>(sc.bases, sc.world, sc.rank, 0, epoch);
+  return check_launch();
+}
+
+int lce_dx_reduce_peer(const lce_problem* p, int64_t row0, int64_t rows, void* workspace, const lce_peer_table* peers,
+                       int32_t dx_dtype, uint32_t epoch, int32_t wait_ms, void* stream) {
+  int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if ((v = check_chunk(p, row0, rows)) != LCE_OK) return v;
+  if (!p->want_grad || !workspace) return LCE_ERR_INVALID_ARGUMENT;
+  if ((v = check_peers(p, peers, dx_dtype)) != LCE_OK) return v;
+  int sms = 0;
+  if ((v = ensure_device(&sms)) != LCE_OK) return v;
+  cudaStream_t st = (cudaStream_t)stream;
+  const Workspace w = layout_workspace(p, workspace, sms);
+  const PeerBases bases = bases_of(peers);
+  const PeerLayout l = layout_peer(p, dx_dtype, w.dx_splits);
+  const int buf = (int)(epoch & 1u);
+  const int rank = peers->rank;
+  // rows of this launch that this rank owns, as indices into its owned slice
+  const long long local0 = row0 % p->chunk_rows;
+  const long long lo = std::max<long long>(local0, (long long)rank * l.rows_own);
+  const long long hi = std::min<long long>(local0 + rows, (long long)(rank + 1) * l.rows_own);
+  const int own_lo = (int)(lo - (long long)rank * l.rows_own);
+  const int own_hi = hi > lo ? (int)(hi - (long long)rank * l.rows_own) : own_lo;
+  unsigned char* mine = bases.base[rank];
+  const uint32_t* flags_a = reinterpret_cast<const uint32_t*>(mine);
+  const float* recv = reinterpret_cast<const float*>(mine + l.recv_off(buf));
+  const long long octs = (long long)(own_hi - own_lo) * (p->hidden / 8);
+  const int grid = grid_for(octs > 0 ? octs : 1, 256, sms, 4);
+  const long long limit = peer_wait_limit_ns(wait_ms);
+  const int ld = (int)hidden_pad(p);
+  switch (dx_dtype) {
+    case LCE_DTYPE_F16:
+      peer_reduce_push_kernel<__half><<<grid, 256, 0, st>>>(bases, peers->world, flags_a, epoch, limit, recv, l.slots,
+                                                            l.rows_own, ld, own_lo, own_hi, rank * l.rows_own,
+                                                            (int)p->hidden, l.stage_off(buf), &w.scalars->status);
+      break;
+    case LCE_DTYPE_BF16:
+      peer_reduce_push_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(bases, peers->world, flags_a, epoch, limit, recv,
+                                                                   l.slots, l.rows_own, ld, own_lo, own_hi,
+                                                                   rank * l.rows_own, (int)p->hidden, l.stage_off(buf),
+                                                                   &w.scalars->status);
+      break;
+    default:
+      peer_reduce_push_kernel<float><<<grid, 256, 0, st>>>(bases, peers->world, flags_a, epoch, limit, recv, l.slots,
+                                                           l.rows_own, ld, own_lo, own_hi, rank * l.rows_own,
+                                                           (int)p->hidden, l.stage_off(buf), &w.scalars->status);
+  }
+  if ((v = check_launch()) != LCE_OK) return v;
+  peer_signal_kernel<<<1, 32, 0, st>>>(bases, peers->world, rank, 1, epoch);
+  return check_launch();
+}
+
+int lce_dx_finish_peer(const lce_problem* p, int64_t row0, int64_t rows, void* workspace, const lce_peer_table* peers,
+                       uint32_t epoch, void* dx, int64_t dx_ld, int32_t dx_dtype, int32_t wait_ms, void* stream) {
+  int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if ((v = check_chunk(p, row0, rows)) != LCE_OK) return v;
+  if (!p->want_grad || !workspace || !dx || dx_ld < p->hidden) return LCE_ERR_INVALID_ARGUMENT;
+  if ((v = check_peers(p, peers, dx_dtype)) != LCE_OK) return v;
+  const int des = elem_size(dx_dtype);
+  if ((reinterpret_cast<uintptr_t>(dx) & 15u) != 0 || ((dx_ld * des) & 15) != 0) return LCE_ERR_MISALIGNED;
+  int sms = 0;
+  if ((v = ensure_device(&sms)) != LCE_OK) return v;
+  cudaStream_t st = (cudaStream_t)stream;
+  const Workspace w = layout_workspace(p, workspace, sms);
+  const PeerLayout l = layout_peer(p, dx_dtype, w.dx_splits);
+  const int buf = (int)(epoch & 1u);
+  unsigned char* mine = reinterpret_cast<unsigned char*>(peers->base[peers->rank]);
+  const uint32_t* flags_b = reinterpret_cast<const uint32_t*>(mine) + kMaxPeers;
+  const long long local0 = row0 % p->chunk_rows;
+  const long long octs = rows * (p->hidden / 8);
+  const int grid = grid_for(octs, 256, sms, 4);
+  const long long limit = peer_wait_limit_ns(wait_ms);
+  char* dx_rows = reinterpret_cast<char*>(dx) + (size_t)row0 * (size_t)dx_ld * des;
+  const unsigned char* stage = mine + l.stage_off(buf);
+  switch (dx_dtype) {
+    case LCE_DTYPE_F16:
+      peer_finish_kernel<__half><<<grid, 256, 0, st>>>(flags_b, peers->world, epoch, limit,
+                                                       reinterpret_cast<const __half*>(stage), (int)local0, (int)rows,
+                                                       (int)p->hidden, reinterpret_cast<__half*>(dx_rows), dx_ld,
+                                                       &w.scalars->status);
+      break;
+    case LCE_DTYPE_BF16:
+      peer_finish_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+          flags_b, peers->world, epoch, limit, reinterpret_cast<const __nv_bfloat16*>(stage), (int)local0, (int)rows,
+          (int)p->hidden, reinterpret_cast<__nv_bfloat16*>(dx_rows), dx_ld, &w.scalars->status);
+      break;
+    default:
+      peer_finish_kernel<float><<<grid, 256, 0, st>>>(flags_b, peers->world, epoch, limit,
+                                                      reinterpret_cast<const float*>(stage), (int)local0, (int)rows,
+                                                      (int)p->hidden, reinterpret_cast<float*>(dx_rows), dx_ld,
+                                                      &w.scalars->status);
   }
   return check_launch();
 }

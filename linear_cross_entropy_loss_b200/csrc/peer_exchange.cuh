@@ -1,0 +1,181 @@
+// Exchange of the dx partials between the GPUs of a vocabulary-sharded run, over peer-mapped memory.
+//
+// Every rank holds one exchange buffer that all ranks of the node can address (NVLink / NVSwitch peer
+// mapping; the caller allocates it and passes the table of base addresses). Layout of one buffer:
+//
+//   [ flags: 2 phases x 8 senders, uint32 ]  (padded to 1 KiB)
+//   [ recv[2] : fp32 [slots][rows_own][h_pad] ]   slots = world * splits, rows_own = chunk_rows / world
+//   [ stage[2]: dx dtype [chunk_rows][hidden] ]
+//
+// One chunk's dx then takes three steps, all of them plain stream-ordered launches:
+//   1. the dx contraction stores every fp32 output tile straight into the recv buffer of the rank that
+//      owns those rows (its epilogue is the sender: the transfer runs tile by tile under the math), then
+//      a one-warp kernel publishes flag A = epoch to every rank;
+//   2. the owner waits for flag A of every sender, sums the slots in a fixed order (rank-major, then
+//      split), rounds once to the dx dtype and stores the rows into the stage buffer of every rank;
+//      a one-warp kernel publishes flag B;
+//   3. every rank waits for flag B of every owner and copies the staged rows into its dx tensor.
+// Only stores and flags cross the links; all loads are local. Each row is summed by exactly one rank and
+// broadcast, so dx is bitwise identical on all ranks and independent of timing.
+//
+// recv/stage are double-buffered by epoch parity so that step 2/3 of one chunk may run on a second
+// stream underneath the next contractions. Epochs grow by one per chunk over the life of the buffer;
+// flags are compared as signed differences.
+//
+// Every wait is bounded by wall time (globaltimer): on expiry the kernel records DEV_WAIT_TIMEOUT_PEER in
+// the status word and returns without touching data; the loss of that pass becomes NaN.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace lce {
+
+constexpr int kMaxPeers = 8;
+constexpr size_t kPeerFlagBytes = 1024;
+enum : int { DEV_WAIT_TIMEOUT_PEER = 104 };
+
+struct PeerBases {
+  unsigned char* base[kMaxPeers];
+};
+
+struct PeerLayout {
+  int slots;           // world * splits
+  int rows_own;        // chunk_rows / world
+  size_t recv_bytes;   // one recv buffer
+  size_t stage_bytes;  // one stage buffer
+  size_t total;
+  __host__ __device__ size_t recv_off(int buf) const { return kPeerFlagBytes + size_t(buf) * recv_bytes; }
+  __host__ __device__ size_t stage_off(int buf) const {
+    return kPeerFlagBytes + 2 * recv_bytes + size_t(buf) * stage_bytes;
+  }
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long wall_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// flag[phase][rank] = epoch in every rank's buffer. Launched after the kernel whose stores it publishes:
+// the kernel boundary orders those stores before this thread, the system-scope fence and release before
+// the flag.
+__global__ void peer_signal_kernel(PeerBases peers, int world, int rank, int phase, uint32_t epoch) {
+  const int t = threadIdx.x;
+  if (t < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(peers.base[t]) + phase * kMaxPeers + rank, epoch);
+  }
+}
+
+// All threads of the CTA call this. Threads 0..world-1 poll one sender's flag each until it has reached
+// `epoch` or `limit_ns` has passed; returns true for the whole CTA iff every flag arrived.
+__device__ __forceinline__ bool peer_wait_all(const uint32_t* flags, int world, uint32_t epoch, long long limit_ns,
+                                              int* status) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const unsigned long long t0 = wall_ns();
+    while (int32_t(ld_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
+      if ((long long)(wall_ns() - t0) > limit_ns) {
+        s_fail = 1;
+        atomicCAS(status, 0, DEV_WAIT_TIMEOUT_PEER);
+        break;
+      }
+      __nanosleep(500);
+    }
+  }
+  __syncthreads();
+  return s_fail == 0;
+}
+
+template <typename T>
+struct Pack8;
+template <>
+struct Pack8<float> {
+  static __device__ __forceinline__ void store(float* dst, const float (&v)[8]) {
+    reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <>
+struct Pack8<__half> {
+  static __device__ __forceinline__ void store(__half* dst, const float (&v)[8]) {
+    __half2 h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(h);
+  }
+};
+template <>
+struct Pack8<__nv_bfloat16> {
+  static __device__ __forceinline__ void store(__nv_bfloat16* dst, const float (&v)[8]) {
+    __nv_bfloat162 h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(h);
+  }
+};
+
+// Step 2: sum the slots of the rows this rank owns and store the result into every rank's stage buffer.
+// recv: this rank's receive buffer [slots][rows_own][ld]; rows [own_lo, own_hi) of it exist in this chunk
+// (indices local to the owned slice); chunk_row0 = chunk-local index of owned row 0.
+template <typename T>
+__global__ void peer_reduce_push_kernel(PeerBases peers, int world, const uint32_t* flags_a, uint32_t epoch,
+                                        long long limit_ns, const float* __restrict__ recv, int slots, int rows_own,
+                                        int ld, int own_lo, int own_hi, int chunk_row0, int hidden,
+                                        size_t stage_off, int* status) {
+  if (!peer_wait_all(flags_a, world, epoch, limit_ns, status)) return;
+  const int octs = hidden >> 3;
+  const long long total = (long long)(own_hi - own_lo) * octs;
+  const size_t slot_stride = size_t(rows_own) * ld;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int r = own_lo + int(i / octs);
+    const int c = int(i % octs) << 3;
+    const float* src = recv + size_t(r) * ld + c;
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int s = 0; s < slots; ++s) {
+      const float4 a = *reinterpret_cast<const float4*>(src + s * slot_stride);
+      const float4 b = *reinterpret_cast<const float4*>(src + s * slot_stride + 4);
+      acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w;
+      acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
+    }
+    const size_t elem = size_t(chunk_row0 + r) * hidden + c;
+    for (int g = 0; g < world; ++g) Pack8<T>::store(reinterpret_cast<T*>(peers.base[g] + stage_off) + elem, acc);
+  }
+}
+
+// Step 3: copy rows [row_lo, row_lo + rows) (chunk-local) of this rank's stage buffer into dx.
+template <typename T>
+__global__ void peer_finish_kernel(const uint32_t* flags_b, int world, uint32_t epoch, long long limit_ns,
+                                   const T* __restrict__ stage, int row_lo, int rows, int hidden, T* __restrict__ dx_rows,
+                                   long long dx_ld, int* status) {
+  if (!peer_wait_all(flags_b, world, epoch, limit_ns, status)) return;
+  const int octs = hidden >> 3;
+  const long long total = (long long)rows * octs;
+  constexpr int kVec = 16 / sizeof(T);  // elements per 16-byte access
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int r = int(i / octs);
+    const int c = int(i % octs) << 3;
+    const T* src = stage + size_t(row_lo + r) * hidden + c;
+    T* dst = dx_rows + (long long)r * dx_ld + c;
+#pragma unroll
+    for (int v = 0; v < 8 / kVec; ++v)
+      reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<const uint4*>(src)[v];
+  }
+}
+
+}  // namespace lce

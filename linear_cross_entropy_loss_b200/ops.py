@@ -94,6 +94,39 @@ class NativeBackend:
             "lce_dx_chunk",
         )
 
+    def peer_bytes(self, prob, dx_dtype) -> int:
+        out = ctypes.c_size_t(0)
+        _native.check(self.lib.lce_peer_bytes(ctypes.byref(prob), _DTYPE_CODE[dx_dtype], ctypes.byref(out)),
+                      "lce_peer_bytes")
+        return int(out.value)
+
+    def dx_chunk_peer(self, prob, At, row0, rows, workspace, table, dx_dtype, epoch):
+        _native.check(
+            self.lib.lce_dx_chunk_peer(
+                ctypes.byref(prob), _ptr(At), At.stride(0), row0, rows, _ptr(workspace), ctypes.byref(table),
+                _DTYPE_CODE[dx_dtype], epoch, self._stream(workspace),
+            ),
+            "lce_dx_chunk_peer",
+        )
+
+    def dx_reduce_peer(self, prob, row0, rows, workspace, table, dx_dtype, epoch, wait_ms=0):
+        _native.check(
+            self.lib.lce_dx_reduce_peer(
+                ctypes.byref(prob), row0, rows, _ptr(workspace), ctypes.byref(table), _DTYPE_CODE[dx_dtype], epoch,
+                wait_ms, self._stream(workspace),
+            ),
+            "lce_dx_reduce_peer",
+        )
+
+    def dx_finish_peer(self, prob, row0, rows, workspace, table, epoch, dx, wait_ms=0):
+        _native.check(
+            self.lib.lce_dx_finish_peer(
+                ctypes.byref(prob), row0, rows, _ptr(workspace), ctypes.byref(table), epoch, _ptr(dx), dx.stride(0),
+                _DTYPE_CODE[dx.dtype], wait_ms, self._stream(workspace),
+            ),
+            "lce_dx_finish_peer",
+        )
+
     def dw_chunk(self, prob, x, row0, rows, workspace, dW_acc, first, dW_final):
         _native.check(
             self.lib.lce_dw_chunk(
@@ -146,6 +179,9 @@ class ShardSpec:
 
     gather_row_parts(local[ROW_PARTS * chunk_rows]) -> all[world * ROW_PARTS * chunk_rows] (rank-major)
     reduce_dx(dx_rows) sums the chunk's dx rows over the ranks, in place.
+    peer_exchange(prob, dx_dtype) -> None or an object with ``table`` (a ``_native.PeerTable``), ``next_epoch()``
+    and ``wait_ms``: when given, dx is exchanged by the contraction's own stores into peer-mapped memory
+    (``lce_dx_chunk_peer`` and friends) and reduce_dx is not called.
     """
 
     rank: int
@@ -153,6 +189,7 @@ class ShardSpec:
     vocab_offset: int
     gather_row_parts: Callable[[torch.Tensor], torch.Tensor]
     reduce_dx: Callable[[torch.Tensor], None]
+    peer_exchange: Optional[Callable] = None
 
 
 # A chunk whose row count allows it is processed as this many sub-chunks, so that the memory-bound slab transform
@@ -237,6 +274,10 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
         side.wait_event(after_event)
         return torch.cuda.stream(side)
 
+    peer = None
+    if shard is not None and want_grad and shard.peer_exchange is not None:
+        peer = shard.peer_exchange(prob, x.dtype)
+
     backend.begin(prob, y, workspace)
     for ci, row0 in enumerate(range(0, N, N_group)):
         rows = min(N_group, N - row0)
@@ -261,6 +302,12 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
             for i, (r0, n) in enumerate(subs):
                 if side is not None:
                     main.wait_event(ready[i])
+                if peer is not None:
+                    epoch = peer.next_epoch()
+                    backend.dx_chunk_peer(prob, At, r0, n, workspace, peer.table, dx.dtype, epoch)
+                    backend.dx_reduce_peer(prob, r0, n, workspace, peer.table, dx.dtype, epoch, peer.wait_ms)
+                    backend.dx_finish_peer(prob, r0, n, workspace, peer.table, epoch, dx, peer.wait_ms)
+                    continue
                 backend.dx_chunk(prob, At, r0, n, workspace, dx)
                 if shard is not None:
                     shard.reduce_dx(dx[r0:r0 + n])

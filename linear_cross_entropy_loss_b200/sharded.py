@@ -9,7 +9,12 @@ and ``y`` are replicated. Per row chunk:
    local kernel merges them in rank order into the global log-sum-exp -- bitwise identical on every
    rank, which a max/sum all-reduce pair would not guarantee;
 3. every rank forms dZ for its slab, its own dW slab (no communication) and a partial dx, which is
-   summed over the ranks with an all-reduce of the chunk's rows (16 MiB at the default shape).
+   summed over the ranks. On the GPUs of one node the dx contraction does that exchange itself
+   (``PeerExchange``): its epilogue stores each fp32 output tile into peer-mapped memory of the rank that
+   owns the rows, the owner adds the tiles of all ranks in a fixed order, rounds once and stores the
+   finished rows back to everyone -- transfers run under the tensor-core work, dx is bitwise identical on
+   all ranks. Otherwise (other backends, shapes the exchange does not take, ``LCE_PEER_DX=0``) the
+   chunk's dx rows are summed with an all-reduce (16 MiB at the default shape).
 
 The reference has no multi-GPU path; the collectives here are NCCL through ``torch.distributed`` (gloo on
 CPU in the unit tests). Loss and metrics come out identical on all ranks.
@@ -23,7 +28,7 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
-from . import ops
+from . import _native, ops
 from ._native import ROW_PARTS
 
 
@@ -60,6 +65,65 @@ class _Collectives:
         self.pending.clear()
 
 
+class PeerExchange:
+    """Peer-mapped exchange buffers (one per rank, symmetric memory) for the dx partials of one process group.
+
+    Built collectively by all ranks of the group on first use for a given size and kept for the life of the
+    process; ``next_epoch`` must advance identically on all ranks, which it does when all ranks run the same
+    sequence of passes.
+    """
+
+    _cache = {}
+    _unavailable = set()
+
+    def __init__(self, group, nbytes: int, device: torch.device):
+        import torch.distributed._symmetric_memory as symm
+
+        pg = group if group is not None else dist.group.WORLD
+        self.buf = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, pg)
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        ptrs = list(self.handle.buffer_ptrs)
+        assert len(ptrs) == world and ptrs[rank] == self.buf.data_ptr()
+        self.table = _native.PeerTable()
+        self.table.world, self.table.rank = world, rank
+        for g in range(world):
+            self.table.base[g] = ptrs[g]
+        self.epoch = 0
+        self.wait_ms = int(os.environ.get("LCE_PEER_WAIT_MS", "0"))
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every rank's flags are zero before anyone signals
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    @classmethod
+    def for_problem(cls, group, prob, dx_dtype, device) -> Optional["PeerExchange"]:
+        """The exchange for this problem, or None when the all-reduce has to be used instead. The decision
+        depends only on values that are equal on all ranks."""
+        backend = ops.get_backend()
+        world = dist.get_world_size(group)
+        if (os.environ.get("LCE_PEER_DX", "1") == "0" or not getattr(backend, "requires_cuda", True)
+                or device.type != "cuda" or world < 2 or world > _native.MAX_PEERS
+                or prob.chunk_rows % (128 * world) != 0):
+            return None
+        gid = id(group) if group is not None else 0
+        if (gid, device.index) in cls._unavailable:
+            return None
+        nbytes = backend.peer_bytes(prob, dx_dtype)
+        key = (gid, device.index, nbytes)
+        if key not in cls._cache:
+            try:
+                cls._cache[key] = cls(group, nbytes, device)
+            except (RuntimeError, ImportError, AssertionError) as err:  # no peer mapping between these GPUs
+                cls._unavailable.add((gid, device.index))
+                print(f"linear_cross_entropy_loss_b200: peer exchange unavailable ({err}); using all-reduce")
+                return None
+        return cls._cache[key]
+
+
 class VocabShardedLinearXent(torch.autograd.Function):
     """Sharded counterpart of ``ops.LinearXentImplementation``: same outputs, W given as this rank's slab."""
 
@@ -74,7 +138,8 @@ class VocabShardedLinearXent(torch.autograd.Function):
             v_local = A.shape[1]
             coll = _Collectives(group, world)
             spec = ops.ShardSpec(rank=rank, world=world, vocab_offset=rank * v_local,
-                                 gather_row_parts=coll.gather_row_parts, reduce_dx=coll.reduce_dx)
+                                 gather_row_parts=coll.gather_row_parts, reduce_dx=coll.reduce_dx,
+                                 peer_exchange=lambda prob, dt: PeerExchange.for_problem(group, prob, dt, x.device))
             want_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[2])
             with torch.no_grad():
                 out5, dx, dA, _ = ops.run_pass(x, y_flat, A, ignore_index, z_regularization, logit_scale,

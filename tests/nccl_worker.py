@@ -24,15 +24,29 @@ def main():
     N, H, V = 1024, 512, 8192
     x, y, W = random_problem(N, H, V, torch.bfloat16, seed=0)
     vl = V // world
-    xd = x.cuda().requires_grad_(True)
-    Ws = W[:, rank * vl:(rank + 1) * vl].contiguous().cuda().requires_grad_(True)
-    out = linear_cross_entropy_sharded(xd, y.cuda(), Ws, None, -1, 1e-4, 0.5, 256, True)
-    out[0].backward()
-    torch.cuda.synchronize()
     ref = oracle.forward_backward(x, y, W, -1, 1e-4, 0.5)
-    ok = abs(out[0].item() - ref.loss) < 2e-5 * ref.loss
-    ok &= cosine(xd.grad.double().cpu().numpy(), ref.dx) > 0.99999
-    ok &= cosine(Ws.grad.double().cpu().numpy(), ref.dW[:, rank * vl:(rank + 1) * vl]) > 0.99999
+    ok = True
+    # dx summed by the contraction's own stores into peer-mapped memory (default), then by an NCCL all-reduce
+    for peer_dx in ("1", "0"):
+        os.environ["LCE_PEER_DX"] = peer_dx
+        xd = x.cuda().requires_grad_(True)
+        Ws = W[:, rank * vl:(rank + 1) * vl].contiguous().cuda().requires_grad_(True)
+        for _ in range(2):  # twice: the second pass reuses the exchange buffers with later epochs
+            xd.grad = Ws.grad = None
+            out = linear_cross_entropy_sharded(xd, y.cuda(), Ws, None, -1, 1e-4, 0.5, 256, True)
+            out[0].backward()
+        torch.cuda.synchronize()
+        ok &= abs(out[0].item() - ref.loss) < 2e-5 * ref.loss
+        ok &= cosine(xd.grad.double().cpu().numpy(), ref.dx) > 0.99999
+        ok &= cosine(Ws.grad.double().cpu().numpy(), ref.dW[:, rank * vl:(rank + 1) * vl]) > 0.99999
+        if peer_dx == "1":
+            from linear_cross_entropy_loss_b200.sharded import PeerExchange
+            ok &= len(PeerExchange._cache) == 1  # the peer path really ran
+            theirs = xd.grad.clone()
+            dist.broadcast(theirs, src=0)
+            ok &= torch.equal(theirs, xd.grad)  # bitwise the same dx on every rank
+        if not ok:
+            print(f"rank {rank}: mismatch with LCE_PEER_DX={peer_dx}", flush=True)
     flag = torch.tensor([1.0 if ok else 0.0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0 and flag.item() == 1.0:

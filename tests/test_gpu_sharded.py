@@ -60,6 +60,79 @@ def test_emulated_shards_on_one_gpu(world):
     assert cosine(dW, ref.dW) > TOL[dtype]["cos"]
 
 
+@pytest.mark.parametrize("world,dtype,N,chunk", [(2, torch.bfloat16, 768, 512), (4, torch.float16, 1024, 512),
+                                                 (8, torch.float32, 2048, 1024), (2, torch.bfloat16, 300, 256)])
+def test_emulated_peer_exchange_of_dx_on_one_gpu(world, dtype, N, chunk):
+    """The dx exchange over peer-mapped memory, with the G ranks' buffers all on this GPU. The ranks are run phase
+    by phase, so every flag a kernel waits for has been published by an earlier launch on the same stream. The
+    result must equal, bit for bit on all ranks, the sum of the per-rank fp32 partials rounded once -- and be at
+    least as close to the oracle as the all-reduce of rounded rows."""
+    H, V = 256, 2048
+    x, y, W = random_problem(N, H, V, dtype, seed=10 + world)
+    xd, yd = x.cuda(), y.cuda()
+    vl = V // world
+    slabs = [W[:, g * vl:(g + 1) * vl].contiguous().cuda() for g in range(world)]
+    be = ops.get_backend()
+    probs = [_native.Problem(n_rows_total=N, chunk_rows=chunk, hidden=H, vocab_local=vl, vocab_offset=g * vl,
+                             ignore_index=-1, world=world, dtype=ops._DTYPE_CODE[dtype], monitoring=0, want_grad=1,
+                             logit_scale=1.0, z_regularization=0.0) for g in range(world)]
+    ws = [torch.empty(be.workspace_bytes(p), dtype=torch.uint8, device="cuda") for p in probs]
+    nbytes = be.peer_bytes(probs[0], dtype)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    tables = []
+    for g in range(world):
+        t = _native.PeerTable()
+        t.world, t.rank = world, g
+        for k in range(world):
+            t.base[k] = bufs[k].data_ptr()
+        tables.append(t)
+    parts = torch.empty(world, 6 * chunk, dtype=torch.float32, device="cuda")
+    dx_peer = [torch.zeros(N, H, dtype=dtype, device="cuda") for _ in range(world)]
+    dx_plain = [torch.zeros(N, H, dtype=torch.float32, device="cuda") for _ in range(world)]
+    for g in range(world):
+        be.begin(probs[g], yd, ws[g])
+    epoch = 0
+    for row0 in range(0, N, chunk):
+        rows = min(chunk, N - row0)
+        epoch += 1
+        for g in range(world):
+            be.forward_chunk(probs[g], xd, slabs[g], yd, row0, rows, ws[g], parts[g])
+        for g in range(world):
+            be.combine_chunk(probs[g], parts, yd, row0, rows, ws[g])
+            be.dz_chunk(probs[g], xd, yd, row0, rows, ws[g])
+            be.dx_chunk(probs[g], slabs[g], row0, rows, ws[g], dx_plain[g])
+            be.dx_chunk_peer(probs[g], slabs[g], row0, rows, ws[g], tables[g], dtype, epoch)
+        for g in range(world):
+            be.dx_reduce_peer(probs[g], row0, rows, ws[g], tables[g], dtype, epoch, 2000)
+        for g in range(world):
+            be.dx_finish_peer(probs[g], row0, rows, ws[g], tables[g], epoch, dx_peer[g], 2000)
+    torch.cuda.synchronize()
+    for g in range(world):
+        assert be.read_status(ws[g]) == 0
+        assert torch.equal(dx_peer[g], dx_peer[0]), "dx must be bitwise identical on all ranks"
+    ref = oracle.forward_backward(x, y, W, -1, 0.0, 1.0)
+    want = sum(d.double() for d in dx_plain)
+    got = dx_peer[0].double()
+    assert cosine(got.cpu().numpy(), ref.dx) > TOL[dtype]["cos"]
+    # one rounding of the fp32 sum: within one unit in the last place of the output type of the fp32 sum
+    eps = {torch.float32: 2.0 ** -22, torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -10}[dtype]
+    mass = sum(d.double().abs() for d in dx_plain)  # fp32 accumulation error is relative to the summed magnitudes
+    tiny = 6e-8 if dtype == torch.float16 else 1e-12  # fp16 gradients of this size are subnormal: absolute spacing 2^-24
+    assert torch.all((got - want).abs() <= eps * want.abs() + 5e-7 * mass + tiny)
+
+
+def test_peer_exchange_refuses_what_it_cannot_do():
+    be = ops.get_backend()
+    prob = _native.Problem(n_rows_total=384, chunk_rows=384, hidden=256, vocab_local=1024, vocab_offset=0,
+                           ignore_index=-1, world=2, dtype=_native.DTYPE_BF16, monitoring=0, want_grad=1,
+                           logit_scale=1.0, z_regularization=0.0)
+    with pytest.raises(_native.LceError):  # 384 rows cannot be split into two owners of whole 128-row tiles
+        be.peer_bytes(prob, torch.bfloat16)
+    prob.chunk_rows, prob.world = 512, 9
+    with pytest.raises(_native.LceError):
+        be.peer_bytes(prob, torch.bfloat16)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_nccl_vocab_sharding_two_gpus():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
