@@ -198,8 +198,8 @@ SUBCHUNKS = 2
 _side_streams: dict = {}
 
 
-def _side_stream(device: torch.device):
-    key = (device.type, device.index)
+def _side_stream(device: torch.device, role: str = "slab"):
+    key = (device.type, device.index, role)
     if key not in _side_streams:
         _side_streams[key] = torch.cuda.Stream(device=device)
     return _side_streams[key]
@@ -278,6 +278,11 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     if shard is not None and want_grad and shard.peer_exchange is not None:
         peer = shard.peer_exchange(prob, x.dtype)
 
+    peer_done = []
+    xstream = None
+    if peer is not None and getattr(peer, "overlap", False):
+        xstream = _side_stream(dev, "exchange")
+
     backend.begin(prob, y, workspace)
     for ci, row0 in enumerate(range(0, N, N_group)):
         rows = min(N_group, N - row0)
@@ -303,10 +308,27 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
                 if side is not None:
                     main.wait_event(ready[i])
                 if peer is not None:
+                    # The contraction scatters its tiles to the owning ranks; the owners' sum, the broadcast and the
+                    # copy into dx follow on a second stream, underneath the next contractions (they wait for other
+                    # ranks, this stream never does). Two epochs may be in flight: one per half of the buffers.
                     epoch = peer.next_epoch()
+                    cur = torch.cuda.current_stream(dev)
+                    if len(peer_done) >= 2:
+                        cur.wait_event(peer_done[-2])
                     backend.dx_chunk_peer(prob, At, r0, n, workspace, peer.table, dx.dtype, epoch)
-                    backend.dx_reduce_peer(prob, r0, n, workspace, peer.table, dx.dtype, epoch, peer.wait_ms)
-                    backend.dx_finish_peer(prob, r0, n, workspace, peer.table, epoch, dx, peer.wait_ms)
+                    if xstream is None:
+                        backend.dx_reduce_peer(prob, r0, n, workspace, peer.table, dx.dtype, epoch, peer.wait_ms)
+                        backend.dx_finish_peer(prob, r0, n, workspace, peer.table, epoch, dx, peer.wait_ms)
+                        continue
+                    scattered = torch.cuda.Event()
+                    scattered.record(cur)
+                    xstream.wait_event(scattered)
+                    with torch.cuda.stream(xstream):
+                        backend.dx_reduce_peer(prob, r0, n, workspace, peer.table, dx.dtype, epoch, peer.wait_ms)
+                        backend.dx_finish_peer(prob, r0, n, workspace, peer.table, epoch, dx, peer.wait_ms)
+                        done = torch.cuda.Event()
+                        done.record(xstream)
+                    peer_done.append(done)
                     continue
                 backend.dx_chunk(prob, At, r0, n, workspace, dx)
                 if shard is not None:
@@ -315,6 +337,8 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
             backend.dw_chunk(prob, x, row0, rows, workspace, dW_acc, ci == 0, dW if last else None)
     if side is not None:
         main.wait_stream(side)
+    if xstream is not None:
+        torch.cuda.current_stream(dev).wait_stream(xstream)
     backend.finalize(prob, workspace, out5)
     return out5, dx, dW, workspace
 

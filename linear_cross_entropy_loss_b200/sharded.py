@@ -9,12 +9,15 @@ and ``y`` are replicated. Per row chunk:
    local kernel merges them in rank order into the global log-sum-exp -- bitwise identical on every
    rank, which a max/sum all-reduce pair would not guarantee;
 3. every rank forms dZ for its slab, its own dW slab (no communication) and a partial dx, which is
-   summed over the ranks. On the GPUs of one node the dx contraction does that exchange itself
-   (``PeerExchange``): its epilogue stores each fp32 output tile into peer-mapped memory of the rank that
-   owns the rows, the owner adds the tiles of all ranks in a fixed order, rounds once and stores the
-   finished rows back to everyone -- transfers run under the tensor-core work, dx is bitwise identical on
-   all ranks. Otherwise (other backends, shapes the exchange does not take, ``LCE_PEER_DX=0``) the
-   chunk's dx rows are summed with an all-reduce (16 MiB at the default shape).
+   summed over the ranks with an all-reduce of the chunk's rows in stream order (16 MiB at the default
+   shape). ``LCE_PEER_DX=1`` selects the device-side exchange instead (``PeerExchange``): the epilogue of
+   the dx contraction stores each fp32 output tile into peer-mapped memory of the rank that owns the
+   rows, the owner adds the tiles of all ranks in a fixed order, rounds once and stores the finished rows
+   back to everyone, on a second stream underneath the next contractions; dx is then bitwise identical
+   on all ranks and rounded once instead of twice. It is not the default because it measured slower on
+   8 x B200 (23.6 against 23.1 ms per step at the default shape, 26.2 against 24.2 ms for N=65536,
+   H=4096): NCCL reduces inside the NVSwitch, while the scattered fp32 tiles cross the links as 32-byte
+   row segments of twice the volume.
 
 The reference has no multi-GPU path; the collectives here are NCCL through ``torch.distributed`` (gloo on
 CPU in the unit tests). Loss and metrics come out identical on all ranks.
@@ -92,6 +95,7 @@ class PeerExchange:
             self.table.base[g] = ptrs[g]
         self.epoch = 0
         self.wait_ms = int(os.environ.get("LCE_PEER_WAIT_MS", "0"))
+        self.overlap = os.environ.get("LCE_PEER_OVERLAP", "1") != "0"
         torch.cuda.synchronize(device)
         dist.barrier(group)  # every rank's flags are zero before anyone signals
 
@@ -105,7 +109,7 @@ class PeerExchange:
         depends only on values that are equal on all ranks."""
         backend = ops.get_backend()
         world = dist.get_world_size(group)
-        if (os.environ.get("LCE_PEER_DX", "1") == "0" or not getattr(backend, "requires_cuda", True)
+        if (os.environ.get("LCE_PEER_DX", "0") != "1" or not getattr(backend, "requires_cuda", True)
                 or device.type != "cuda" or world < 2 or world > _native.MAX_PEERS
                 or prob.chunk_rows % (128 * world) != 0):
             return None
