@@ -9,6 +9,7 @@ from .ops import (  # noqa: F401
     bwd_configs,
     fwd_configs,
     linear_cross_entropy,
+    set_autocast_policy,
 )
 
-__all__ = ["LinearCrossEntropyLoss", "linear_cross_entropy", "fwd_configs", "bwd_configs"]
+__all__ = ["LinearCrossEntropyLoss", "linear_cross_entropy", "fwd_configs", "bwd_configs", "set_autocast_policy"]

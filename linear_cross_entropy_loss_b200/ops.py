@@ -403,7 +403,86 @@ class LinearXentImplementation(torch.autograd.Function):
         return gx, None, gA, None, None, None, None, None
 
 
-@torch.compiler.disable  # the kernels are reached through ctypes: under torch.compile this call runs eagerly
+# ------------------------------------------------------------------------------------------------
+# torch.library registration: the same pass as ONE opaque operator, so that torch.compile / export can
+# trace through a model that contains the loss without a graph break (the reference cannot be traced:
+# its author lists this as open, reference ops.py:706 and README). Eager calls keep using the
+# autograd.Function above; the operator is picked while a compiler is tracing.
+# ------------------------------------------------------------------------------------------------
+@torch.library.custom_op("lce_b200::fused_pass", mutates_args=())
+def fused_pass_op(x: torch.Tensor, y: torch.Tensor, At: torch.Tensor, ignore_index: int, z_regularization: float,
+                  logit_scale: float, N_chunk_size: int, monitoring: bool,
+                  want_grad: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(out5, dx, dW): out5 = float32[5] (loss, z_value, logit_max, logit_entropy, logit_norm); the gradients of the
+    loss with respect to x and At (empty tensors without want_grad)."""
+    with _device_guard(x):
+        x2, y_flat, A = _prepare(x, y, At)
+        out5, dx, dA, _ = run_pass(x2, y_flat, A, ignore_index, z_regularization, logit_scale, N_chunk_size,
+                                   monitoring, want_grad)
+    if not want_grad:
+        return out5, x.new_empty(0), At.new_empty(0)
+    return out5, dx.view(x.shape), dA
+
+
+@fused_pass_op.register_fake
+def _fused_pass_fake(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size, monitoring, want_grad):
+    out5 = x.new_empty(5, dtype=torch.float32)
+    if not want_grad:
+        return out5, x.new_empty(0), At.new_empty(0)
+    return out5, x.new_empty(x.shape), At.new_empty(At.shape)
+
+
+def _fused_pass_setup(ctx, inputs, output):
+    ctx.lce_want_grad = inputs[-1]
+    ctx.save_for_backward(output[1], output[2])
+
+
+def _fused_pass_backward(ctx, grad_out5, grad_dx, grad_dW):
+    if not ctx.lce_want_grad:
+        raise RuntimeError("the fused loss was traced without gradients")
+    dx, dW = ctx.saved_tensors
+    g = grad_out5[0]  # only the loss is differentiable (reference ops.py:804-810)
+    return (dx * g).to(dx.dtype), None, (dW * g).to(dW.dtype), None, None, None, None, None, None
+
+
+fused_pass_op.register_autograd(_fused_pass_backward, setup_context=_fused_pass_setup)
+
+# What CUDA autocast does to the inputs: "reference" = cast to fp16 whatever the autocast dtype is, as the
+# reference does (ops.py:665-667); "follow" = cast to the autocast dtype (bf16 autocast -> bf16 kernels).
+_AUTOCAST_POLICY = "reference"
+
+
+def set_autocast_policy(policy: str) -> None:
+    global _AUTOCAST_POLICY
+    assert policy in ("reference", "follow")
+    _AUTOCAST_POLICY = policy
+
+
+def _autocast_target(x) -> Optional[torch.dtype]:
+    if not x.is_cuda or not torch.is_autocast_enabled("cuda"):
+        return None
+    return torch.float16 if _AUTOCAST_POLICY == "reference" else torch.get_autocast_dtype("cuda")
+
+
+def _apply(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size, monitoring):
+    """The 5-tuple of the reference's autograd function, through the operator that fits the calling context."""
+    if torch.compiler.is_compiling():
+        target = _autocast_target(x)
+        if target is not None:
+            x, At = x.to(target), At.to(target)
+        want_grad = torch.is_grad_enabled() and (x.requires_grad or At.requires_grad)
+        out5, _, _ = fused_pass_op(x, y, At, int(ignore_index), float(z_regularization), float(logit_scale),
+                                   int(N_chunk_size), bool(monitoring), want_grad)
+        return out5[0], out5[1].detach(), out5[2].detach(), out5[3].detach(), out5[4].detach()
+    if _AUTOCAST_POLICY == "follow" and _autocast_target(x) is not None:
+        target = _autocast_target(x)
+        with torch.autocast(device_type="cuda", enabled=False):
+            return LinearXentImplementation.apply(x.to(target), y, At.to(target), ignore_index, z_regularization,
+                                                  logit_scale, N_chunk_size, monitoring)
+    return LinearXentImplementation.apply(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size,
+                                          monitoring)
+
+
 def linear_cross_entropy(
     x,
     y,
@@ -415,9 +494,7 @@ def linear_cross_entropy(
     monitoring: bool = False,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """Functional form (reference ops.py:814-826): returns (loss, z_value, logit_max, logit_entropy, logit_norm)."""
-    return LinearXentImplementation.apply(
-        x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size, monitoring
-    )  # type: ignore
+    return _apply(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size, monitoring)  # type: ignore
 
 
 class LinearCrossEntropyLoss(torch.nn.Linear):
@@ -480,9 +557,8 @@ class LinearCrossEntropyLoss(torch.nn.Linear):
             std = math.sqrt(1 / self.in_features)
             torch.nn.init.trunc_normal_(self.weight, mean=0.0, std=std, a=-3 * std, b=3 * std)
 
-    @torch.compiler.disable  # runs eagerly inside a compiled model (graph break around the ctypes calls)
     def forward(self, x, y):
-        loss, z_reg, logit_max, logit_ent, logit_norm = LinearXentImplementation.apply(
+        loss, z_reg, logit_max, logit_ent, logit_norm = _apply(
             x, y, self.weight, self.ignore_index, self.z_regularization, self.logit_scale, self.N_chunk_size,
             self.monitoring,
         )  # type: ignore

@@ -233,6 +233,50 @@ def test_autocast_casts_inputs_to_fp16_like_the_reference():
     assert cosine(xd.grad.double().cpu().numpy(), ref.dx) > 0.999999
 
 
+def test_autocast_policy_follow_uses_the_autocast_dtype():
+    import linear_cross_entropy_loss_b200 as pkg
+
+    x, y, W = random_problem(256, 256, 512, torch.float32, seed=15)
+    xd = x.cuda().requires_grad_(True)
+    Wd = W.cuda().requires_grad_(True)
+    pkg.set_autocast_policy("follow")
+    try:
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = linear_cross_entropy(xd, y.cuda(), Wd, -1)[0]
+        loss.backward()
+    finally:
+        pkg.set_autocast_policy("reference")
+    assert xd.grad.dtype == torch.float32 and Wd.grad.dtype == torch.float32
+    ref = oracle.forward_backward(x.bfloat16(), y, W.bfloat16(), -1)  # bf16-rounded inputs, not fp16-rounded ones
+    assert abs(loss.item() - ref.loss) < 2e-5 * ref.loss
+    assert cosine(xd.grad.double().cpu().numpy(), ref.dx) > 0.99999
+    ref16 = oracle.forward_backward(x.half(), y, W.half(), -1)
+    assert abs(loss.item() - ref16.loss) > abs(loss.item() - ref.loss)
+
+
+def test_traced_by_torch_compile_without_a_graph_break():
+    """The pass is registered as one torch.library operator, so a compiled model contains it as a single node."""
+    torch.manual_seed(0)
+    head = LinearCrossEntropyLoss(256, 1024, ignore_index=-1, N_chunk_size=256).cuda().bfloat16()
+    h = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = torch.randint(0, 1024, (512,), device="cuda")
+    eager = head(h, y)
+    eager.backward()
+    g_h, g_w = h.grad.clone(), head.weight.grad.clone()
+    h.grad = head.weight.grad = None
+    compiled = torch.compile(lambda a, b: head(torch.tanh(a) + a, b) * 3.0, backend="aot_eager", fullgraph=True)
+    plain = head(torch.tanh(h) + h, y) * 3.0
+    plain.backward()
+    want_h, want_w = h.grad.clone(), head.weight.grad.clone()
+    h.grad = head.weight.grad = None
+    out = compiled(h, y)
+    out.backward()
+    assert abs(out.item() - plain.item()) < 1e-6 * abs(plain.item())
+    assert torch.allclose(h.grad.float(), want_h.float(), rtol=2e-2, atol=1e-6)
+    assert torch.allclose(head.weight.grad.float(), want_w.float(), rtol=2e-2, atol=1e-6)
+    assert g_h is not None and g_w is not None
+
+
 def test_device_status_is_clean_after_a_pass():
     from linear_cross_entropy_loss_b200 import ops
     x, y, W = random_problem(256, 256, 512, torch.bfloat16, seed=15)

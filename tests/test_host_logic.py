@@ -146,7 +146,7 @@ def test_custom_init_method_is_used():
     assert torch.all(m.weight == 0.25)
 
 
-def test_module_inside_torch_compile_runs_eagerly(fake):
+def test_module_inside_torch_compile(fake):
     class Head(torch.nn.Module):
         def __init__(self):
             super().__init__()
@@ -161,10 +161,27 @@ def test_module_inside_torch_compile_runs_eagerly(fake):
     h = torch.randn(256, 64)
     y = torch.randint(0, 200, (256,))
     eager = head(h, y)
-    compiled = torch.compile(head, backend="eager")(h, y)
+    eager.backward()
+    want = [head.proj.weight.grad.clone(), head.loss.weight.grad.clone()]
+    head.zero_grad()
+    # fullgraph: the pass is one torch.library operator (lce_b200::fused_pass), so tracing meets no graph break
+    compiled = torch.compile(head, backend="aot_eager", fullgraph=True)(h, y)
     assert abs(eager.item() - compiled.item()) < 1e-6
-    compiled.backward()
-    assert head.proj.weight.grad is not None and head.loss.weight.grad is not None
+    (compiled * 2).backward()
+    assert torch.allclose(head.proj.weight.grad, 2 * want[0], atol=1e-7)
+    assert torch.allclose(head.loss.weight.grad, 2 * want[1], atol=1e-7)
+    with torch.no_grad():  # traced without gradients: the gradient kernels are not part of the graph
+        before = len(fake.calls)
+        again = torch.compile(head, backend="aot_eager", fullgraph=True)(h, y)
+        assert abs(again.item() - eager.item()) < 1e-6
+        assert "dx_chunk" not in fake.calls[before:]
+
+
+def test_autocast_policy_switch():
+    ops.set_autocast_policy("follow")
+    ops.set_autocast_policy("reference")
+    with pytest.raises(AssertionError):
+        ops.set_autocast_policy("bf16")
 
 
 def test_export_names_of_the_reference_package():
