@@ -403,7 +403,42 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr
     tmem_ld_wait();
     const int lim = ncols - c * 32;
     float r[32];
-    if (!row_ok || lim <= 0) {
+    if (p.peer_rows_own > 0) {
+      // Scatter to the owning rank (whole padded tiles, so no masks). A thread holds 128 contiguous bytes of
+      // ITS row, and storing them as they are gives 32 separate 32-byte segments per warp instruction, which a
+      // link to another GPU carries poorly. So the four lanes of a group first exchange 32-byte units --
+      // round t sends unit (q ^ t) to lane ^ t, after which lane q holds unit q of all four rows of its
+      // group -- and then store row by row: each instruction writes 128 contiguous bytes of 8 rows.
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] = coef * __uint_as_float(v[i]);
+      const int lane = row_in_tile & 31;
+      const int q = lane & 3;
+      float got[4][8];  // got[t] = unit q of row (lane ^ t)
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int u = q ^ t;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float lo = (u & 1) ? r[8 + k] : r[k];
+          const float hi = (u & 1) ? r[24 + k] : r[16 + k];
+          const float send = (u & 2) ? hi : lo;
+          got[t][k] = (t == 0) ? send : __shfl_xor_sync(0xffffffffu, send, t);
+        }
+      }
+      float* group_row0 = dst - (long long)q * p.out_ld + c * 32 + 8 * q;  // row (lane & ~3), this lane's unit
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = q ^ j;  // the round in which row (lane & ~3) + j arrived
+        uint32_t o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float lo = (t & 1) ? got[1][k] : got[0][k];
+          const float hi = (t & 1) ? got[3][k] : got[2][k];
+          o[k] = __float_as_uint((t & 2) ? hi : lo);
+        }
+        st_global_256(group_row0 + (long long)j * p.out_ld, o);
+      }
+    } else if (!row_ok || lim <= 0) {
       // nothing of this chunk exists in the output
     } else if (lim >= 32 && p.out_vector_ok) {
       // whole chunk inside the output and 32-byte accesses allowed
