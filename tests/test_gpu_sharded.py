@@ -121,6 +121,36 @@ def test_emulated_peer_exchange_of_dx_on_one_gpu(world, dtype, N, chunk):
     assert torch.all((got - want).abs() <= eps * want.abs() + 5e-7 * mass + tiny)
 
 
+def test_peer_wait_runs_out_and_reports_instead_of_hanging():
+    """A flag that nothing sets: the bounded wait gives up after wait_ms, copies nothing, and the status word turns
+    the loss of the pass into NaN. (No fault is provoked: the kernel returns normally.)"""
+    be = ops.get_backend()
+    N = H = 256
+    prob = _native.Problem(n_rows_total=N, chunk_rows=256, hidden=H, vocab_local=512, vocab_offset=0, ignore_index=-1,
+                           world=2, dtype=_native.DTYPE_BF16, monitoring=0, want_grad=1, logit_scale=1.0,
+                           z_regularization=0.0)
+    ws = torch.empty(be.workspace_bytes(prob), dtype=torch.uint8, device="cuda")
+    y = torch.zeros(N, dtype=torch.int64, device="cuda")
+    be.begin(prob, y, ws)
+    bufs = [torch.zeros(be.peer_bytes(prob, torch.bfloat16), dtype=torch.uint8, device="cuda") for _ in range(2)]
+    table = _native.PeerTable()
+    table.world, table.rank = 2, 0
+    table.base[0], table.base[1] = bufs[0].data_ptr(), bufs[1].data_ptr()
+    dx = torch.full((N, H), 7.0, dtype=torch.bfloat16, device="cuda")
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    be.dx_finish_peer(prob, 0, N, ws, table, 1, dx, 200)  # nobody ever publishes flag B of epoch 1
+    t1.record()
+    torch.cuda.synchronize()
+    assert 150 < t0.elapsed_time(t1) < 2000
+    assert be.read_status(ws) == -6  # LCE_ERR_DEVICE_TIMEOUT
+    assert torch.all(dx == 7.0)
+    out5 = torch.zeros(5, dtype=torch.float32, device="cuda")
+    be.finalize(prob, ws, out5)
+    assert torch.isnan(out5[0])
+
+
 def test_peer_exchange_refuses_what_it_cannot_do():
     be = ops.get_backend()
     prob = _native.Problem(n_rows_total=384, chunk_rows=384, hidden=256, vocab_local=1024, vocab_offset=0,
