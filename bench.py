@@ -212,6 +212,9 @@ def config_dict(cfg, n_gpus, args):
                     f"z_regularization={cfg.z_regularization} monitoring={cfg.monitoring}",
         "N": cfg.N, "H": cfg.H, "V": cfg.V, "N_chunk_size": cfg.N_chunk_size,
         "vocab_sharding": f"{n_gpus} x {cfg.V // n_gpus} columns" if n_gpus > 1 else "none",
+        "dx_exchange": ("none" if n_gpus == 1 else
+                        "peer stores fused into the dx contraction" if os.environ.get("LCE_PEER_DX") == "1"
+                        else "NCCL all-reduce per chunk, in stream order"),
         "l2": "inputs larger than L2 (the weight alone is >= 512 MiB per GPU); no explicit flush",
         "gemm_variant": "single-CTA 128x256 tiles" if getattr(args, "gemm_variant", 0) & 1 else "CTA-pair 256x256 tiles",
     }
