@@ -39,7 +39,7 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 # forward 381.9 MB, dx 931.7 MB, dW 406.5 MB. Forward and dx traffic grow in proportion to V; the figures are scaled
 # by V_local / 32768 at run time (only for N_chunk_size=4096, H=2048, which the capture used). dW is not scaled: from
 # the second chunk on it also reads and rewrites the fp32 accumulator, which the one-chunk capture does not contain.
-NCU_DRAM_BYTES_V32768 = {"fwd": 381.9e6, "dx": 931.7e6, "dw": None}
+NCU_DRAM_BYTES_V32768 = {"fwd": 391.4e6, "dx": 738.5e6, "dw": None}
 
 
 def parse_args():
