@@ -312,14 +312,15 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
                     # copy into dx follow on a second stream, underneath the next contractions (they wait for other
                     # ranks, this stream never does). Two epochs may be in flight: one per half of the buffers.
                     epoch = peer.next_epoch()
+                    if xstream is None:  # everything in order on one stream
+                        backend.dx_chunk_peer(prob, At, r0, n, workspace, peer.table, dx.dtype, epoch)
+                        backend.dx_reduce_peer(prob, r0, n, workspace, peer.table, dx.dtype, epoch, peer.wait_ms)
+                        backend.dx_finish_peer(prob, r0, n, workspace, peer.table, epoch, dx, peer.wait_ms)
+                        continue
                     cur = torch.cuda.current_stream(dev)
                     if len(peer_done) >= 2:
                         cur.wait_event(peer_done[-2])
                     backend.dx_chunk_peer(prob, At, r0, n, workspace, peer.table, dx.dtype, epoch)
-                    if xstream is None:
-                        backend.dx_reduce_peer(prob, r0, n, workspace, peer.table, dx.dtype, epoch, peer.wait_ms)
-                        backend.dx_finish_peer(prob, r0, n, workspace, peer.table, epoch, dx, peer.wait_ms)
-                        continue
                     scattered = torch.cuda.Event()
                     scattered.record(cur)
                     xstream.wait_event(scattered)

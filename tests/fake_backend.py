@@ -70,6 +70,26 @@ class FakeBackend:
         coef = prob.logit_scale / st["n_valid"]
         dx[row0:row0 + rows] = torch.from_numpy(st["dz"][row0] @ At.double().numpy().T * coef).to(dx.dtype)
 
+    # The dx exchange over peer memory, for one rank: the "exchange buffer" is a dict keyed by epoch.
+    def peer_bytes(self, prob, dx_dtype):
+        return 4096
+
+    def dx_chunk_peer(self, prob, At, row0, rows, workspace, table, dx_dtype, epoch):
+        self.calls.append(("dx_chunk_peer", epoch))
+        st = self.state[workspace.data_ptr()]
+        coef = prob.logit_scale / st["n_valid"]
+        assert epoch not in table.scattered and len(table.scattered) < 2, "at most two epochs in flight"
+        table.scattered[epoch] = torch.from_numpy(st["dz"][row0] @ At.double().numpy().T * coef)
+
+    def dx_reduce_peer(self, prob, row0, rows, workspace, table, dx_dtype, epoch, wait_ms=0):
+        self.calls.append(("dx_reduce_peer", epoch))
+        table.reduced[epoch] = table.scattered[epoch].to(dx_dtype)
+
+    def dx_finish_peer(self, prob, row0, rows, workspace, table, epoch, dx, wait_ms=0):
+        self.calls.append(("dx_finish_peer", epoch))
+        dx[row0:row0 + rows] = table.reduced.pop(epoch)
+        del table.scattered[epoch]
+
     def dw_chunk(self, prob, x, row0, rows, workspace, dW_acc, first, dW_final):
         self.calls.append("dw_chunk")
         st = self.state[workspace.data_ptr()]

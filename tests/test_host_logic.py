@@ -177,6 +177,40 @@ def test_module_inside_torch_compile(fake):
         assert "dx_chunk" not in fake.calls[before:]
 
 
+def test_peer_exchange_sequencing_in_the_chunk_loop(fake):
+    """With a peer exchange in the shard description the loop calls scatter / reduce / finish per chunk with
+    consecutive epochs (continuing over passes) instead of dx_chunk + reduce_dx, and gives the same gradients."""
+    class Table:
+        scattered, reduced = {}, {}
+
+    class Exchange:
+        table, wait_ms, overlap, epoch = Table(), 0, False, 40
+
+        def next_epoch(self):
+            self.epoch += 1
+            return self.epoch
+
+    ex = Exchange()
+    reduce_calls = []
+    x, y, W = make(N=640, H=256, V=512)
+    want = oracle.forward_backward(x, y, W, -1)
+    for n_pass in range(2):
+        shard = ops.ShardSpec(rank=0, world=1, vocab_offset=0, gather_row_parts=lambda t: t,
+                              reduce_dx=reduce_calls.append, peer_exchange=lambda prob, dt: ex)
+        out5, dx, dW, _ = ops.run_pass(x, y, W, -1, 0.0, 1.0, 256, False, True, shard=shard)
+        assert np.allclose(dx.numpy(), want.dx, atol=2e-7) and np.allclose(dW.numpy(), want.dW, atol=2e-7)
+    assert reduce_calls == [] and "dx_chunk" not in fake.calls
+    peer_calls = [c for c in fake.calls if isinstance(c, tuple)]
+    assert peer_calls == [(name, e) for e in range(41, 47)
+                          for name in ("dx_chunk_peer", "dx_reduce_peer", "dx_finish_peer")]
+    # without gradients the exchange is not even asked for
+    asked = []
+    shard = ops.ShardSpec(rank=0, world=1, vocab_offset=0, gather_row_parts=lambda t: t, reduce_dx=reduce_calls.append,
+                          peer_exchange=lambda prob, dt: asked.append(1))
+    ops.run_pass(x, y, W, -1, 0.0, 1.0, 256, False, False, shard=shard)
+    assert asked == []
+
+
 def test_autocast_policy_switch():
     ops.set_autocast_policy("follow")
     ops.set_autocast_policy("reference")
