@@ -14,10 +14,11 @@ and ``y`` are replicated. Per row chunk:
    the dx contraction stores each fp32 output tile into peer-mapped memory of the rank that owns the
    rows, the owner adds the tiles of all ranks in a fixed order, rounds once and stores the finished rows
    back to everyone, on a second stream underneath the next contractions; dx is then bitwise identical
-   on all ranks and rounded once instead of twice. It is not the default because it measured slower on
-   8 x B200 (23.6 against 23.1 ms per step at the default shape, 26.2 against 24.2 ms for N=65536,
-   H=4096): NCCL reduces inside the NVSwitch, while the scattered fp32 tiles cross the links as 32-byte
-   row segments of twice the volume.
+   on all ranks and rounded once instead of twice. Measured on 8 x B200 it is 1 % faster than the all-reduce
+   at the default shape (22.24 against 22.48 ms per step), equal on 2 and 4 GPUs, and 2.5 % slower when the
+   slab per rank is small (N=65536, H=4096, 16384 columns per rank: 24.33 against 23.73 ms): NCCL reduces
+   inside the NVSwitch, the scatter moves fp32 partials of twice the volume. It needs 0.3 GB of peer-mapped
+   memory per rank, so it is opt-in.
 
 The reference has no multi-GPU path; the collectives here are NCCL through ``torch.distributed`` (gloo on
 CPU in the unit tests). Loss and metrics come out identical on all ranks.
