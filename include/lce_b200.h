@@ -62,7 +62,21 @@ typedef struct lce_problem {
   int32_t want_grad;      /* 0: forward only (no slab is written)                  */
   float logit_scale;      /* z = logit_scale * (x @ W)  (ops.py:200)               */
   float z_regularization; /* weight of mean(lse^2)       (ops.py:756-761)          */
+  int32_t slab_mode;      /* LCE_SLAB_* : how the exponentials kept between forward and backward are normalised */
+  int32_t reserved;       /* must be 0                                             */
 } lce_problem;
+
+/* slab_mode. The forward keeps exp(z - b) of the chunk in the element type of the inputs (the "slab").
+ * LCE_SLAB_DEFAULT: bf16 / fp32 use ONE base b per row, found from a two-tile probe, which makes the backward a
+ *   plain contraction with a per-row factor; a row group whose logits fall outside the window around its base
+ *   (row max - base outside about [-60, +72]) is recomputed. fp16 uses LCE_SLAB_PER_TILE (its exponent range
+ *   is too narrow for one base per row).
+ * LCE_SLAB_PER_TILE: b = the maximum of each (row, 256-column tile); lce_dz_chunk then rewrites the slab in
+ *   place once. Never recomputes; the better choice for bf16 / fp32 when the logits of a row spread over more
+ *   than about 100 units, where the default mode would recompute most chunks. All calls of a pass must use the
+ *   same mode. */
+#define LCE_SLAB_DEFAULT 0
+#define LCE_SLAB_PER_TILE 1
 
 /* Number of per-row partial statistics a rank exports per chunk (base b of the sums, sum exp(z - b),
  * target logit, sum exp(z - b) z, sum z^2, max z); lce_forward_chunk writes LCE_ROW_PARTS * chunk_rows floats. */
@@ -180,6 +194,12 @@ int lce_dx_finish_peer(const lce_problem* p, int64_t row0, int64_t rows, void* w
  * tuple, ops.py:802). The last three are only meaningful with monitoring. If any kernel of the pass
  * reported a device-side error the loss is NaN. */
 int lce_finalize(const lce_problem* p, void* workspace, float* out5, void* stream);
+
+/* How often the default slab mode had to recompute in the pass that used `workspace`: copies two int32
+ * {256-row groups recomputed, 256-row groups processed} to host_out2, asynchronously on `stream` when host_out2 is
+ * pinned memory (valid once the stream has passed this point; nothing synchronises). A caller that sees a large
+ * fraction should run its next passes of that shape with LCE_SLAB_PER_TILE. No counterpart in the reference. */
+int lce_rerun_stats_async(void* workspace, int32_t* host_out2, void* stream);
 
 /* dst[r, c] = src[r, c] * (*dev_factor), converting element type (the reference's
  * x_grad.mul_(grad_output), ops.py:810). cols % 8 == 0. src == dst is allowed when the types match, and

@@ -51,6 +51,8 @@ class Problem(ctypes.Structure):
         ("want_grad", ctypes.c_int32),
         ("logit_scale", ctypes.c_float),
         ("z_regularization", ctypes.c_float),
+        ("slab_mode", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
     ]
 
 
@@ -101,6 +103,7 @@ _i32 = ctypes.c_int32
 _u32 = ctypes.c_uint32
 
 MAX_PEERS = 8
+SLAB_DEFAULT, SLAB_PER_TILE = 0, 1
 
 
 class PeerTable(ctypes.Structure):
@@ -137,6 +140,7 @@ SIGNATURES = {
     "lce_finalize": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _vp, _vp]),
     "lce_grad_scale_cast": (ctypes.c_int, [_vp, _i32, _i64, _vp, _i32, _i64, _i64, _i64, _vp, _vp]),
     "lce_read_status": (ctypes.c_int, [_vp, _vp]),
+    "lce_rerun_stats_async": (ctypes.c_int, [_vp, _vp, _vp]),
     "lce_eval_loss_static": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _vp, _vp, _vp]),
     "lce_set_gemm_variant": (ctypes.c_int, [_i32]),
     "lce_profile_enable": (ctypes.c_int, [_i32]),

@@ -25,6 +25,8 @@ struct PassScalars {
   float n_valid;     // number of rows whose label is not ignore_index
   int status;        // device status word, 0 = ok
   int rescue;        // row-reference mode: set when a row's max logit is more than kRefRange from its reference
+  int rerun_groups;  // row-reference mode: 256-row groups of this pass whose forward had to be recomputed ...
+  int seen_groups;   // ... out of this many (what a caller needs to pick the slab mode of its next pass)
 };
 
 // Per-row partials a rank exports per chunk:
@@ -87,6 +89,8 @@ __global__ void begin_kernel(const long long* __restrict__ labels, long long n, 
     sc->n_valid = (float)total;
     sc->status = 0;
     sc->rescue = 0;
+    sc->rerun_groups = 0;
+    sc->seen_groups = 0;
   }
 }
 
@@ -266,7 +270,12 @@ combine_kernel(const float* __restrict__ parts_all, int world, const long long* 
     sc->sum_norm += t_norm;
     sc->max_logit = fmaxf(sc->max_logit, t_max);
     sc->rescue = 0;  // the chunk's conditional re-run (if any) is behind us
+    int flagged = 0;
+    for (int g = 0; g < n_groups; ++g) flagged += rescue_groups[g] != 0;
+    sc->rerun_groups += flagged;
+    sc->seen_groups += (rows + 255) >> 8;
   }
+  __syncthreads();
   for (int g = threadIdx.x; g < n_groups; g += blockDim.x) rescue_groups[g] = 0;
 }
 

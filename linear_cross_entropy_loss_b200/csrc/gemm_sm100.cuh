@@ -110,6 +110,7 @@ struct GemmParams {
   int run_mask_row0;
 
   int* status;                 // device status word (0 = ok)
+  int tile_mode;               // forward epilogue: 1 = exp(z - tile max) even for bf16 / fp32
   long long* clock_probe;      // optional [2]: SM cycles and nanoseconds CTA 0 spent in the kernel (diagnostics)
   // EPI_F32 scatter mode (peer_rows_own > 0): the output rows are spread over the receive buffers of the ranks
   // that own them -- rank o owns chunk rows [o * peer_rows_own, (o + 1) * peer_rows_own) -- and split s of
@@ -359,7 +360,7 @@ __device__ __forceinline__ void epilogue_forward_rowref(const GemmParams& p, uin
   }
 }
 
-// fp16 slabs are normalised per tile, bf16 / fp32 slabs per row.
+// fp16 slabs are always normalised per tile; bf16 / fp32 slabs per row unless the launch asks for tiles.
 template <int kKind>
 struct ForwardMode {
   static constexpr bool kRowRef = (kKind != KIND_F16);
@@ -368,7 +369,7 @@ struct ForwardMode {
 template <int kKind, bool kMonitor>
 __device__ __forceinline__ void epilogue_forward(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk,
                                                  int row_in_tile) {
-  if (ForwardMode<kKind>::kRowRef)
+  if (ForwardMode<kKind>::kRowRef && !p.tile_mode)
     epilogue_forward_rowref<kKind, kMonitor>(p, taddr, m_blk, n_blk, row_in_tile);
   else
     epilogue_forward_tilemax<kKind, kMonitor>(p, taddr, m_blk, n_blk, row_in_tile);

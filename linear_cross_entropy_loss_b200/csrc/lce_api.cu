@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cstddef>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -112,6 +113,8 @@ int validate_problem(const lce_problem* p) {
   if (p->n_rows_total <= 0 || p->chunk_rows <= 0 || p->hidden <= 0 || p->vocab_local <= 0)
     return LCE_ERR_INVALID_ARGUMENT;
   if (p->world < 1 || p->vocab_offset < 0) return LCE_ERR_INVALID_ARGUMENT;
+  if ((p->slab_mode != LCE_SLAB_DEFAULT && p->slab_mode != LCE_SLAB_PER_TILE) || p->reserved != 0)
+    return LCE_ERR_INVALID_ARGUMENT;
   if (!(p->logit_scale > 0.f) || !(p->z_regularization >= 0.f)) return LCE_ERR_INVALID_ARGUMENT;
   if (p->chunk_rows % BLOCK_M != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
   // rows of x and W must start on 16-byte boundaries (TMA) and are handled 8 elements at a time
@@ -164,7 +167,9 @@ struct Workspace {
 
 // fp16 slabs hold exp(z - tile max) and are rescaled in a separate pass; bf16 / fp32 slabs hold
 // exp(z - row reference) and feed the gradient GEMMs directly (see gemm_sm100.cuh).
-inline bool row_reference_mode(const lce_problem* p) { return p->dtype != LCE_DTYPE_F16; }
+inline bool row_reference_mode(const lce_problem* p) {
+  return p->dtype != LCE_DTYPE_F16 && p->slab_mode != LCE_SLAB_PER_TILE;
+}
 
 Workspace layout_workspace(const lce_problem* p, void* base, int sms) {
   Workspace w;
@@ -423,6 +428,7 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
   gp.rows_valid = (int)rows;
   gp.cols_valid = (int)p->vocab_local;
   gp.store_slab = (p->want_grad && w.slab != nullptr) ? 1 : 0;
+  gp.tile_mode = row_reference_mode(p) ? 0 : 1;
   gp.tile_max = w.tile_max + local0;
   gp.tile_sum = w.tile_sum + local0;
   gp.tile_ez = w.tile_ez + local0;
@@ -986,6 +992,16 @@ int lce_read_status(void* workspace, void* stream) {
     return LCE_ERR_CUDA;
   if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) return LCE_ERR_CUDA;
   return host.status == 0 ? LCE_OK : LCE_ERR_DEVICE_TIMEOUT;
+}
+
+int lce_rerun_stats_async(void* workspace, int32_t* host_out2, void* stream) {
+  if (!workspace || !host_out2) return LCE_ERR_INVALID_ARGUMENT;
+  const PassScalars* sc = reinterpret_cast<const PassScalars*>(workspace);
+  static_assert(offsetof(PassScalars, seen_groups) == offsetof(PassScalars, rerun_groups) + sizeof(int), "pair");
+  if (cudaMemcpyAsync(host_out2, &sc->rerun_groups, 2 * sizeof(int), cudaMemcpyDeviceToHost,
+                      (cudaStream_t)stream) != cudaSuccess)
+    return LCE_ERR_CUDA;
+  return LCE_OK;
 }
 
 int lce_set_gemm_variant(int32_t variant) {

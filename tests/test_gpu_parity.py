@@ -277,6 +277,47 @@ def test_traced_by_torch_compile_without_a_graph_break():
     assert g_h is not None and g_w is not None
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_per_tile_slab_mode_for_bf16_and_fp32(dtype, monkeypatch):
+    """LCE_SLAB_PER_TILE (exp(z - tile max) + one in-place slab pass) gives the same results as the default
+    one-base-per-row mode, including sub-chunks on two streams, ragged shapes, and logits far outside the window
+    of the default mode (where it never recomputes)."""
+    monkeypatch.setenv("LCE_SLAB_MODE", "tile")
+    x, y, W = random_problem(2048, 256, 2048, dtype, seed=31)
+    check_against_oracle(x, y, W, dtype, ignore=-1, zreg=1e-4, scale=0.5, chunk=1024)        # two sub-chunks per chunk
+    x, y, W = random_problem(600, 264, 1000, dtype, seed=32)
+    check_against_oracle(x, y, W, dtype, ignore=-1, chunk=256)                               # ragged everything
+    x, y, W = random_problem(512, 256, 4096, torch.bfloat16, seed=33)
+    check_against_oracle(x.to(dtype), y, W.to(dtype), dtype, ignore=-1, scale=64.0, chunk=256)  # logit spread ~ 64
+
+
+def test_slab_mode_policy_switches_after_passes_that_recompute(monkeypatch):
+    """auto: a shape whose passes recompute most row groups moves to the per-tile mode once the counters of a
+    finished pass have arrived (polled, never waited for), and narrow logits of the same shape stay in the default
+    mode. Results are right in either mode."""
+    from linear_cross_entropy_loss_b200 import _native, ops
+
+    monkeypatch.delenv("LCE_SLAB_MODE", raising=False)
+    policy = ops.slab_mode_policy
+    policy.history.clear()
+    x, y, W = random_problem(1024, 256, 4096, torch.bfloat16, seed=34)
+    key = (torch.cuda.current_device(), torch.bfloat16, 256, 4096, 512, 1)
+    # wide logits (spread ~ 100): every row group leaves the window
+    check_against_oracle(x, y, W, torch.bfloat16, ignore=-1, scale=100.0, chunk=512)
+    torch.cuda.synchronize()
+    assert policy.choose(key, torch.bfloat16) == _native.SLAB_PER_TILE
+    assert policy.history[key]["fraction"] > 0.9
+    check_against_oracle(x, y, W, torch.bfloat16, ignore=-1, scale=100.0, chunk=512)    # this one ran per tile
+    # another shape with LM-like logits: stays in the default mode
+    x2, y2, W2 = random_problem(1024, 256, 2048, torch.bfloat16, seed=35)
+    key2 = (torch.cuda.current_device(), torch.bfloat16, 256, 2048, 512, 1)
+    check_against_oracle(x2, y2, W2, torch.bfloat16, ignore=-1, chunk=512)
+    torch.cuda.synchronize()
+    assert policy.choose(key2, torch.bfloat16) == _native.SLAB_DEFAULT
+    assert policy.history[key2]["fraction"] == 0.0
+    policy.history.clear()
+
+
 def test_device_status_is_clean_after_a_pass():
     from linear_cross_entropy_loss_b200 import ops
     x, y, W = random_problem(256, 256, 512, torch.bfloat16, seed=15)
