@@ -228,7 +228,8 @@ class SlabModePolicy:
     ``LCE_SLAB_MODE=row|tile`` fixes the mode; ``auto`` (default) starts in the default mode, reads -- without
     ever synchronising: a pinned-memory copy plus an event that is only polled -- how many row groups the last
     finished pass of the same shape recomputed, switches to per-tile above ``threshold`` and tries the default
-    mode again every ``retry_every`` passes.
+    mode again every ``retry_every`` passes. Polling an event is not allowed while a stream is being captured
+    into a CUDA graph: fix the mode with ``LCE_SLAB_MODE`` when capturing passes.
     """
 
     threshold = 0.25
