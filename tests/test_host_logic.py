@@ -211,6 +211,42 @@ def test_peer_exchange_sequencing_in_the_chunk_loop(fake):
     assert asked == []
 
 
+def test_slab_mode_policy_decisions(monkeypatch):
+    """The mode picker on its own: fp16 always per tile; bf16 per row until a finished pass reported that more
+    than a quarter of its row groups were recomputed; a retry of the default mode every 64th pass; env overrides."""
+    from linear_cross_entropy_loss_b200 import _native
+
+    class DoneEvent:
+        def query(self):
+            return True
+
+    class PendingEvent:
+        def query(self):
+            return False
+
+    monkeypatch.delenv("LCE_SLAB_MODE", raising=False)
+    pol = ops.SlabModePolicy()
+    key = (0, torch.bfloat16, 2048, 131072, 4096, 1)
+    assert pol.choose(key, torch.float16) == _native.SLAB_PER_TILE
+    assert pol.choose(key, torch.bfloat16) == _native.SLAB_DEFAULT            # nothing known yet
+    pol.history[key] = {"host": torch.tensor([12, 16], dtype=torch.int32), "event": PendingEvent(), "fraction": 0.0,
+                        "tile_passes": 0}
+    assert pol.choose(key, torch.bfloat16) == _native.SLAB_DEFAULT            # counters not there yet: no waiting
+    pol.history[key]["event"] = DoneEvent()
+    assert pol.choose(key, torch.bfloat16) == _native.SLAB_PER_TILE           # 12 of 16 groups recomputed
+    assert pol.history[key]["fraction"] == 0.75 and pol.history[key]["event"] is None
+    modes = [pol.choose(key, torch.bfloat16) for _ in range(130)]
+    assert modes.count(_native.SLAB_DEFAULT) == 2                               # passes 64 and 128 probe the default mode
+    pol.history[key].update(host=torch.tensor([1, 16], dtype=torch.int32), event=DoneEvent())
+    assert pol.choose(key, torch.float32) == _native.SLAB_DEFAULT              # 1 of 16: back to one base per row
+    monkeypatch.setenv("LCE_SLAB_MODE", "tile")
+    assert pol.choose(key, torch.bfloat16) == _native.SLAB_PER_TILE
+    monkeypatch.setenv("LCE_SLAB_MODE", "row")
+    pol.history[key]["fraction"] = 1.0
+    assert pol.choose(key, torch.bfloat16) == _native.SLAB_DEFAULT
+    assert pol.choose(key, torch.float16) == _native.SLAB_PER_TILE
+
+
 def test_autocast_policy_switch():
     ops.set_autocast_policy("follow")
     ops.set_autocast_policy("reference")
