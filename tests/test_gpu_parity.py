@@ -318,6 +318,28 @@ def test_slab_mode_policy_switches_after_passes_that_recompute(monkeypatch):
     policy.history.clear()
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_randomised_shapes_options_and_modes(seed, monkeypatch):
+    """Seeded random draws of shape, chunking, options, dtype and slab mode against the oracle."""
+    rng = np.random.default_rng(1000 + seed)
+    dtype = [torch.bfloat16, torch.float16, torch.float32][seed % 3]
+    monkeypatch.setenv("LCE_SLAB_MODE", ["row", "tile", "auto"][(seed // 3) % 3])
+    N = int(rng.integers(1, 1400))
+    H = 8 * int(rng.integers(1, 80))
+    V = 8 * int(rng.integers(1, 700))
+    chunk = int(rng.choice([128, 200, 256, 512, 1024, 4096]))
+    scale = float(rng.choice([0.25, 1.0, 3.0]))
+    zreg = float(rng.choice([0.0, 1e-4, 1e-2]))
+    ignore = int(rng.choice([-100, -1, 5]))
+    x, y, W = random_problem(N, H, V, dtype, seed=2000 + seed, ignore=ignore, frac=float(rng.choice([0.0, 0.1, 0.6])))
+    y[0] = (5 % V) if ignore != 5 else 6 % V  # at least one valid row
+    # The tensor core truncates fp32 operands to TF32 (it does not round them), which shrinks every logit by up to
+    # 2^-10 relative: a bias of the loss that grows with the logit scale (measured 5e-4 at scale 3).
+    loss_tol = 1e-3 if dtype == torch.float32 else None
+    check_against_oracle(x, y, W, dtype, ignore=ignore, zreg=zreg, scale=scale, chunk=chunk,
+                         monitoring=bool(seed % 2), loss_tol=loss_tol)
+
+
 def test_device_status_is_clean_after_a_pass():
     from linear_cross_entropy_loss_b200 import ops
     x, y, W = random_problem(256, 256, 512, torch.bfloat16, seed=15)
