@@ -12,6 +12,16 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100a); run with -m gpu on the GPU box")
 
 
+@pytest.fixture(autouse=True)
+def fresh_slab_mode_history():
+    """Every test starts with the default slab mode: what earlier tests' passes recomputed must not pick the mode of
+    this one (the policy remembers shapes for the life of the process)."""
+    from linear_cross_entropy_loss_b200 import ops
+
+    ops.slab_mode_policy.history.clear()
+    yield
+
+
 @pytest.fixture(scope="session")
 def golden():
     import numpy as np
