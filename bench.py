@@ -158,6 +158,13 @@ def cpu_reference_rate(cfg, seconds, steps=1, warmup=0):
     from oracle import oracle
 
     torch.manual_seed(0)
+    # all host cores this process may use (torchrun exports OMP_NUM_THREADS=1 for multi-rank launches)
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    if torch.get_num_threads() < avail:
+        torch.set_num_threads(avail)
     cores = torch.get_num_threads()
     V = min(cfg.V, 131072)
     H = cfg.H
