@@ -392,7 +392,7 @@ def main():
         base = NCU_DRAM_BYTES_V32768.get(dominant)
         traffic = (base * v_local / 32768.0) if (base and cfg.H == 2048 and min(cfg.N, cfg.N_chunk_size) == 4096) \
             else None
-        roofline = {"bound": "tensor", "kernel": f"lce_gemm_kernel[{dominant}]", "achieved": achieved,
+        roofline = {"bound": "tensor", "kernel": ("lce_gemm_kernel" if getattr(args, "gemm_variant", 0) & 1 else "lce_gemm_pair_kernel") + f"[{dominant}]", "achieved": achieved,
                     "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved / peak_tflops,
                     "peak_source": f"{peak_source} cuBLAS bf16 GEMM, sustained",
                     "traffic": traffic,
