@@ -39,6 +39,33 @@ def test_every_entry_point_cites_the_reference_or_says_it_has_no_counterpart():
     assert "No counterpart in the reference" in HEADER
 
 
+def test_header_is_plain_c_and_the_ctypes_mirrors_have_its_layout(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 on its own, and the ctypes structures must have the
+    size and field offsets the C compiler gives lce_problem and lce_peer_table."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    fields_p = [f[0] for f in _native.Problem._fields_]
+    fields_t = [f[0] for f in _native.PeerTable._fields_]
+    src = tmp_path / "layout.c"
+    lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{ROOT / "include" / "lce_b200.h"}"', "int main(void) {",
+             '  printf("%zu\\n", sizeof(lce_problem));']
+    lines += [f'  printf("%zu\\n", offsetof(lce_problem, {f}));' for f in fields_p]
+    lines += ['  printf("%zu\\n", sizeof(lce_peer_table));']
+    lines += [f'  printf("%zu\\n", offsetof(lce_peer_table, {f}));' for f in fields_t]
+    lines += ["  return 0;", "}"]
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-pedantic", "-o", str(exe), str(src)], check=True)
+    got = [int(v) for v in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    want = [ctypes.sizeof(_native.Problem)] + [getattr(_native.Problem, f).offset for f in fields_p]
+    want += [ctypes.sizeof(_native.PeerTable)] + [getattr(_native.PeerTable, f).offset for f in fields_t]
+    assert got == want
+
+
 def test_version_and_status_strings(lib):
     assert lib.lce_version() >= 100
     assert _native.status_string(0) == "ok"
