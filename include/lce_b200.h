@@ -19,9 +19,10 @@
  *   - W is stored (hidden, vocab) with the vocab index contiguous, like the reference's
  *     transposed nn.Linear weight (ops.py:913).
  *
- * Shapes: any number of rows; hidden % 8 == 0 and vocab_local % 8 == 0 (rows of x and W start on 16-byte
- * boundaries); chunk_rows % 128 == 0. The kernels work on 128 x 256 tiles: what hangs over the edges is
- * zero-filled on load and masked on store. (The reference asserts N % 512, V % 4096, H % 256: ops.py:689-691.)
+ * Shapes: any number of rows and any vocabulary size; hidden % 8 == 0; chunk_rows % 128 == 0. The rows of x, W and
+ * dW must start on 16-byte boundaries (LCE_ERR_MISALIGNED otherwise): for a vocabulary size that is not a multiple
+ * of 8 give W and dW a row stride rounded up to 8 elements. The kernels work on 128 x 256 tiles: what hangs over
+ * the edges is zero-filled on load and masked on store. (The reference asserts N % 512, V % 4096, H % 256: ops.py:689-691.)
  */
 #ifndef LCE_B200_H
 #define LCE_B200_H

@@ -117,8 +117,9 @@ int validate_problem(const lce_problem* p) {
     return LCE_ERR_INVALID_ARGUMENT;
   if (!(p->logit_scale > 0.f) || !(p->z_regularization >= 0.f)) return LCE_ERR_INVALID_ARGUMENT;
   if (p->chunk_rows % BLOCK_M != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
-  // rows of x and W must start on 16-byte boundaries (TMA) and are handled 8 elements at a time
-  if (p->hidden % 8 != 0 || p->vocab_local % 8 != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
+  // rows of x are handled 8 elements at a time. The vocabulary may have any size: columns past it are masked in
+  // every epilogue; only the ROWS of W and dW must start on 16-byte boundaries (checked where they are used).
+  if (p->hidden % 8 != 0) return LCE_ERR_UNSUPPORTED_SHAPE;
   // TMA coordinates and the kernels' tile counters are 32-bit
   if (p->n_rows_total > (1ll << 30) || p->hidden > (1ll << 30) || p->vocab_local > (1ll << 30))
     return LCE_ERR_TOO_LARGE;

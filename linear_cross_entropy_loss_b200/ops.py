@@ -145,10 +145,12 @@ class NativeBackend:
         )
 
     def grad_scale_cast(self, src, dst, factor):
+        cols = -(-src.shape[1] // 8) * 8  # whole groups of 8: the padding columns of an aligned-rows buffer go along
+        assert cols <= src.stride(0) and cols <= dst.stride(0)
         _native.check(
             self.lib.lce_grad_scale_cast(
                 _ptr(src), _DTYPE_CODE[src.dtype], src.stride(0), _ptr(dst), _DTYPE_CODE[dst.dtype], dst.stride(0),
-                src.shape[0], src.shape[1], _ptr(factor), self._stream(src),
+                src.shape[0], cols, _ptr(factor), self._stream(src),
             ),
             "lce_grad_scale_cast",
         )
@@ -307,7 +309,6 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     assert x.dtype in _DTYPE_CODE, f"unsupported dtype {x.dtype}"
     assert y.dtype == torch.int64, "labels must be int64"
     assert N >= 1, "x must have at least one row"
-    assert V % 8 == 0, "the (local) vocabulary size must be divisible by 8"
     assert H % 8 == 0, "the hidden size must be divisible by 8"
     assert logit_scale > 0 and z_regularization >= 0
     assert int(N_chunk_size) >= 1
@@ -333,9 +334,9 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     dx = dW = dW_acc = None
     if want_grad:
         dx = torch.empty((N, H), dtype=x.dtype, device=dev)
-        dW = torch.empty((H, V), dtype=At.dtype, device=dev)
+        dW = _aligned_rows_like((H, V), At.dtype, dev)
         if n_chunks > 1:  # fp32 accumulator across chunks; the last chunk writes dW from it
-            dW_acc = torch.empty((H, V), dtype=torch.float32, device=dev)
+            dW_acc = _aligned_rows_like((H, V), torch.float32, dev)
 
     # second stream only where sub-chunks exist (per-tile slabs); everything else runs in order on the caller's stream
     use_side = native and dev.type == "cuda" and per_tile and want_grad and SUBCHUNKS == 2
@@ -425,15 +426,30 @@ def _device_guard(t: torch.Tensor):
     return torch.cuda.device(t.device) if t.is_cuda else contextlib.nullcontext()
 
 
+def _aligned_rows_like(shape, dtype, device):
+    """An uninitialised (rows, cols) tensor whose rows start on 16-byte boundaries: a view of a buffer that is a few
+    columns wider when cols is not a multiple of 8 (vocabulary sizes such as 50257)."""
+    rows, cols = shape
+    ld = -(-cols // 8) * 8  # whole groups of 8 elements: 16 bytes for 16-bit types, 32 for fp32 (vector accesses)
+    buf = torch.empty((rows, ld), dtype=dtype, device=device)
+    return buf if ld == cols else buf[:, :cols]
+
+
+def _tma_ready(t):
+    return t.stride(-1) == 1 and (t.stride(0) * t.element_size()) % 16 == 0 and t.data_ptr() % 16 == 0
+
+
 def _prepare(x_in, y, At):
     x = x_in.reshape(-1, x_in.shape[-1])
-    if x.stride(-1) != 1 or (x.stride(0) * x.element_size()) % 16 != 0:
+    if not _tma_ready(x):
         x = x.contiguous()
     y = y.reshape(-1)
     if not y.is_contiguous():
         y = y.contiguous()
-    if At.stride(-1) != 1 or (At.stride(0) * At.element_size()) % 16 != 0:
-        At = At.contiguous()
+    if not _tma_ready(At):  # e.g. a vocabulary size that is not a multiple of 8: copy into 16-byte aligned rows
+        copy = _aligned_rows_like(At.shape, At.dtype, At.device)
+        copy.copy_(At)
+        At = copy
     return x, y, At
 
 
@@ -586,7 +602,7 @@ class LinearCrossEntropyLoss(torch.nn.Linear):
     ``logit_norm``, ``logit_max``, ``logit_entropy`` and ``z_value``, defined as in the reference's
     ``reference_torch`` (ops.py:9-17).
 
-    Differences from the reference, all of them relaxations: any number of rows, H % 8 and V % 8 (the
+    Differences from the reference, all of them relaxations: any number of rows, H % 8 and any V (the
     reference needs N % 512, H % 256, V % 4096), there is no autotuning on the first call, and gradients are
     only computed when an input requires them.
     """
@@ -607,7 +623,7 @@ class LinearCrossEntropyLoss(torch.nn.Linear):
         torch.nn.Module.__init__(self)  # not nn.Linear.__init__: no bias, transposed weight
 
         assert in_features % 8 == 0
-        assert out_features % 8 == 0
+        assert out_features >= 1
         assert N_chunk_size >= 1
         assert logit_scale > 0
         assert z_regularization >= 0

@@ -66,6 +66,11 @@ def test_header_is_plain_c_and_the_ctypes_mirrors_have_its_layout(tmp_path):
     assert got == want
 
 
+def test_any_vocabulary_size_is_a_valid_problem(lib):
+    rc, nbytes = workspace_bytes(lib, problem(vocab_local=4001))
+    assert rc == 0 and nbytes > 0
+
+
 def test_version_and_status_strings(lib):
     assert lib.lce_version() >= 100
     assert _native.status_string(0) == "ok"
@@ -105,7 +110,7 @@ def test_workspace_size_accounts_for_slab_statistics_and_partials(lib):
 @pytest.mark.parametrize("kw,code", [
     (dict(dtype=7), -1), (dict(hidden=0), -1), (dict(logit_scale=0.0), -1), (dict(z_regularization=-1.0), -1),
     (dict(world=0), -1), (dict(n_rows_total=0), -1),
-    (dict(hidden=100), -2), (dict(vocab_local=4001), -2), (dict(chunk_rows=192), -2),
+    (dict(hidden=100), -2), (dict(chunk_rows=192), -2), (dict(slab_mode=5), -1), (dict(reserved=1), -1),
     (dict(vocab_local=1 << 31), -8),
 ])
 def test_invalid_problems_are_rejected_without_a_device(lib, kw, code):

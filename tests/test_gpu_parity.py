@@ -88,6 +88,23 @@ def test_shapes_that_are_not_multiples_of_the_tiles(dtype, N, H, V, chunk):
     check_against_oracle(x, y, W, dtype, ignore=-1, zreg=1e-4, scale=0.75, chunk=chunk)
 
 
+@pytest.mark.parametrize("dtype,N,H,V,chunk", [(torch.bfloat16, 300, 264, 1001, 256), (torch.float16, 512, 256, 4099, 256),
+                                                (torch.float32, 200, 64, 777, 128), (torch.bfloat16, 130, 128, 3, 128),
+                                                (torch.bfloat16, 1024, 256, 50257 // 8, 512)])
+def test_vocabulary_sizes_that_are_not_multiples_of_8(dtype, N, H, V, chunk):
+    """Tokenizer vocabularies (50257, 32001, ...) are odd: W and dW then live in buffers whose rows are padded to
+    16 bytes, the vocabulary itself is not padded (columns past V are masked in the kernels)."""
+    x, y, W = random_problem(N, H, V, dtype, seed=V)
+    got, dxn, dWn, ref = check_against_oracle(x, y, W, dtype, ignore=-1, zreg=1e-4, scale=0.5, chunk=chunk)
+    assert dWn.shape == (H, V)
+    # grad_output != 1 scales through the padded rows as well
+    xd = x.cuda().requires_grad_(True)
+    Wd = W.cuda().requires_grad_(True)
+    (linear_cross_entropy(xd, y.cuda(), Wd, -1, 1e-4, 0.5, chunk)[0] * 3.0).backward()
+    assert Wd.grad.shape == (H, V)
+    assert cosine(Wd.grad.double().cpu().numpy(), 3.0 * ref.dW) > TOL[dtype]["cos"]
+
+
 def test_labels_on_tile_boundaries_and_repeated_labels():
     x, y, W = random_problem(256, 256, 1024, torch.float16, seed=5, frac=0.0)
     y[:8] = torch.tensor([0, 255, 256, 511, 512, 767, 768, 1023])

@@ -92,8 +92,9 @@ def test_shape_and_dtype_checks(fake):
     x, y, W = make()
     with pytest.raises(AssertionError):
         linear_cross_entropy(x[:, :100], y, W[:100])
-    with pytest.raises(AssertionError):
-        linear_cross_entropy(x, y, W[:, :100])
+    y100 = y.clamp(max=99)
+    out = linear_cross_entropy(x, y100, W[:, :100].clone().requires_grad_(True), -1)  # any vocabulary size is taken
+    assert abs(out[0].item() - oracle.forward_backward(x, y100, W[:, :100], -1, want_grad=False).loss) < 1e-5
     with pytest.raises(AssertionError):
         linear_cross_entropy(x, y.int(), W)
     with pytest.raises(AssertionError):
@@ -133,7 +134,8 @@ def test_module_surface_matches_the_reference(fake):
 
 
 def test_module_constructor_asserts():
-    for bad in [dict(in_features=100), dict(out_features=1001), dict(N_chunk_size=0), dict(logit_scale=0.0),
+    assert LinearCrossEntropyLoss(256, 1001).weight.shape == (256, 1001)  # any vocabulary size
+    for bad in [dict(in_features=100), dict(out_features=0), dict(N_chunk_size=0), dict(logit_scale=0.0),
                 dict(z_regularization=-1.0)]:
         kw = dict(in_features=256, out_features=512)
         kw.update(bad)
