@@ -118,3 +118,17 @@ def test_peak_extra_memory_stays_below_one_fp32_chunk_of_logits():
     budget = cfg.N_chunk_size * cfg.V * 4               # one fp32 chunk of logits: the reference's stated peak
     assert peak - fp32_accumulator - grads <= budget, (peak, fp32_accumulator, grads, budget)
     assert peak <= 1.5 * budget
+
+
+def test_slab_modes_agree_at_the_default_point(monkeypatch):
+    """bf16 at full size: one base per row and per-tile slabs are two routes to the same dZ."""
+    cfg = synthetic.CONFIGS["headline_bf16"]
+    x, y, W = synthetic.make_inputs(cfg, device="cuda")
+    monkeypatch.setenv("LCE_SLAB_MODE", "row")
+    got_r, dx_r, dW_r = run(cfg, x, y, W)
+    monkeypatch.setenv("LCE_SLAB_MODE", "tile")
+    got_t, dx_t, dW_t = run(cfg, x, y, W)
+    assert abs(got_r[0] - got_t[0]) <= 2e-6 * abs(got_r[0]), (got_r[0], got_t[0])
+    cos = torch.nn.functional.cosine_similarity
+    assert cos(dx_r.double().flatten(), dx_t.double().flatten(), dim=0).item() > 0.99999
+    assert cos(dW_r.double().flatten(), dW_t.double().flatten(), dim=0).item() > 0.99999
