@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--config", default="headline_bf16")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--n-chunk-size", type=int, default=0,
+                    help="override the configuration's N_chunk_size (0 = keep it; the metric's point uses 4096)")
     ap.add_argument("--gemm-variant", type=int, default=0, choices=[0, 1, 2, 3],
                     help="A/B measurement bits: 1 = single-CTA kernels instead of CTA pairs, 2 = dx tiles M-first")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1, rank 0)")
@@ -246,6 +248,8 @@ def main():
 
     n_gpus = max(args.gpus, world)
     base = synthetic.CONFIGS[args.config]
+    if args.n_chunk_size > 0:
+        base = synthetic.scaled(base, N_chunk_size=args.n_chunk_size, name=f"{base.name}_chunk{args.n_chunk_size}")
     cfg = base
     if n_gpus > 1 and args.scaling == "weak":
         cfg = synthetic.scaled(base, V=base.V * n_gpus, name=f"{base.name}_x{n_gpus}vocab")

@@ -559,6 +559,11 @@ def _autocast_target(x) -> Optional[torch.dtype]:
 
 def _apply(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size, monitoring):
     """The 5-tuple of the reference's autograd function, through the operator that fits the calling context."""
+    if not torch.is_grad_enabled():
+        # Evaluation under torch.no_grad() with a trainable weight: inside autograd.Function.forward the inputs still
+        # look as if they needed gradients, so the gradient kernels would run for nothing (as they do in the
+        # reference, which always computes them). Detached inputs select the forward-only pass.
+        x, At = x.detach(), At.detach()
     if torch.compiler.is_compiling():
         target = _autocast_target(x)
         if target is not None:

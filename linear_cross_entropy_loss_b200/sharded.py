@@ -173,6 +173,8 @@ def linear_cross_entropy_sharded(x, y, At_shard, group=None, ignore_index=-100, 
     Returns the same 5-tuple on every rank. ``x.grad`` is the full gradient (summed over the shards),
     ``At_shard.grad`` is the gradient of this rank's slab.
     """
+    if not torch.is_grad_enabled():  # evaluation under torch.no_grad(): forward-only pass (see ops._apply)
+        x, At_shard = x.detach(), At_shard.detach()
     return VocabShardedLinearXent.apply(x, y, At_shard, group, ignore_index, z_regularization, logit_scale,
                                         N_chunk_size, monitoring)
 

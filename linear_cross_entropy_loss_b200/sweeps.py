@@ -1,7 +1,7 @@
 """Speed, peak-memory and accuracy sweeps of the fused loss over N, H and V.
 
     python -m linear_cross_entropy_loss_b200.sweeps --mode speed|memory|accuracy [--over N H V]
-           [--acc bf16 fp16 fp16-mixed] [--out DIR] [--quick]
+           [--acc bf16 fp16 fp16-mixed] [--out DIR] [--quick] [--forward-only]
 
 Re-creates the three sweep families of the reference's benchmark script (bench_fusions.py:210-226 speed,
 :318-334 memory, :448-467 accuracy of the reference project) around its default point N=16384, H=2048,
@@ -58,22 +58,29 @@ def _inputs(N, H, V, acc, low_loss: bool, seed=0):
     return x.to(dtype).requires_grad_(True), y, At
 
 
-def speed_point(N, H, V, acc, reps):
+def speed_point(N, H, V, acc, reps, forward_only=False):
     x, y, At = _inputs(N, H, V, acc, low_loss=False)
+
+    def step():
+        if forward_only:  # evaluation: nothing requires grad, so no slab is written and no gradient kernel runs
+            with torch.no_grad():
+                _call(x, y, At, acc)
+        else:
+            _call(x, y, At, acc).backward()
+            x.grad = At.grad = None
+
     for _ in range(3):
-        _call(x, y, At, acc).backward()
-        x.grad = At.grad = None
+        step()
     times = []
     for _ in range(reps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        _call(x, y, At, acc).backward()
+        step()
         e1.record()
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1))
-        x.grad = At.grad = None
     ms = statistics.median(times)
-    flop = 3 * (2 * N * H * V + 3 * N * V)
+    flop = (1 if forward_only else 3) * (2 * N * H * V + 3 * N * V)
     return flop * 1e-12 / (ms * 1e-3)
 
 
@@ -147,8 +154,14 @@ def main():
     ap.add_argument("--out", default="sweeps_out")
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--quick", action="store_true", help="every other point of each range")
+    ap.add_argument("--forward-only", action="store_true",
+                    help="speed mode: time the loss under torch.no_grad() (one third of the flop count); CSVs go to "
+                         "bench-fwd/ (the reference has no such sweep)")
     args = ap.parse_args()
     out = Path(args.out) / {"speed": "bench", "memory": "bench-mem", "accuracy": "bench-acc"}[args.mode]
+    if args.forward_only:
+        assert args.mode == "speed", "--forward-only goes with --mode speed"
+        out = Path(args.out) / "bench-fwd"
 
     for acc in args.acc:
         for var in args.over:
@@ -161,7 +174,8 @@ def main():
                 shape[var] = 2 ** e
                 try:
                     if args.mode == "speed":
-                        rows.append((shape[var], speed_point(shape["N"], shape["H"], shape["V"], acc, args.reps)))
+                        rows.append((shape[var], speed_point(shape["N"], shape["H"], shape["V"], acc, args.reps,
+                                                             args.forward_only)))
                     elif args.mode == "memory":
                         rows.append((shape[var], memory_point(shape["N"], shape["H"], shape["V"], acc)))
                     else:

@@ -69,6 +69,15 @@ def test_no_gradient_work_without_requires_grad(fake):
     assert "dx_chunk" not in fake.calls and "dw_chunk" not in fake.calls
     assert not out[0].requires_grad
     assert abs(out[0].item() - oracle.forward_backward(x, y, W, -1, want_grad=False).loss) < 1e-5
+    # evaluation under torch.no_grad() with tensors that do require grad (a trainable weight): forward only as well
+    fake.calls.clear()
+    xr, Wr = x.clone().requires_grad_(True), W.clone().requires_grad_(True)
+    with torch.no_grad():
+        out2 = linear_cross_entropy(xr, y, Wr, ignore_index=-1)
+        m = LinearCrossEntropyLoss(256, 768, ignore_index=-1)
+        m(x, y)
+    assert "dx_chunk" not in fake.calls and "dw_chunk" not in fake.calls and "dz_chunk" not in fake.calls
+    assert abs(out2[0].item() - out[0].item()) < 1e-7
 
 
 def test_leading_dimensions_are_flattened_and_grad_keeps_the_input_shape(fake):
