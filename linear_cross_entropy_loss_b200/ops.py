@@ -298,6 +298,10 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     to a second stream, underneath the tensor-core kernels of the other.
     """
     backend = get_backend()
+    # want_grad: a bool, or (gradient for x wanted, gradient for the weight wanted) -- a frozen head or frozen
+    # features skip the contraction whose result nobody asks for (a third of the pass each)
+    want_dx, want_dW = (want_grad, want_grad) if isinstance(want_grad, bool) else (bool(want_grad[0]), bool(want_grad[1]))
+    want_grad = want_dx or want_dW
     native = getattr(backend, "requires_cuda", True)
     if native and not (x.is_cuda and y.is_cuda and At.is_cuda):
         raise RuntimeError("linear_cross_entropy_loss_b200 runs on CUDA tensors only; there is no CPU fallback")
@@ -332,8 +336,9 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     row_parts = torch.empty(ROW_PARTS * N_group, dtype=torch.float32, device=dev)
     out5 = torch.empty(5, dtype=torch.float32, device=dev)
     dx = dW = dW_acc = None
-    if want_grad:
+    if want_dx:
         dx = torch.empty((N, H), dtype=x.dtype, device=dev)
+    if want_dW:
         dW = _aligned_rows_like((H, V), At.dtype, dev)
         if n_chunks > 1:  # fp32 accumulator across chunks; the last chunk writes dW from it
             dW_acc = _aligned_rows_like((H, V), torch.float32, dev)
@@ -350,7 +355,7 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
         return torch.cuda.stream(side)
 
     peer = None
-    if shard is not None and want_grad and shard.peer_exchange is not None:
+    if shard is not None and want_dx and shard.peer_exchange is not None:
         peer = shard.peer_exchange(prob, x.dtype)
 
     peer_done = []
@@ -382,6 +387,8 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
             for i, (r0, n) in enumerate(subs):
                 if side is not None:
                     main.wait_event(ready[i])
+                if not want_dx:
+                    continue
                 if peer is not None:
                     # The contraction scatters its tiles to the owning ranks; the owners' sum, the broadcast and the
                     # copy into dx follow on a second stream, underneath the next contractions (they wait for other
@@ -410,7 +417,8 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
                 if shard is not None:
                     shard.reduce_dx(dx[r0:r0 + n])
             last = ci == n_chunks - 1
-            backend.dw_chunk(prob, x, row0, rows, workspace, dW_acc, ci == 0, dW if last else None)
+            if want_dW:
+                backend.dw_chunk(prob, x, row0, rows, workspace, dW_acc, ci == 0, dW if last else None)
     if side is not None:
         main.wait_stream(side)
     if xstream is not None:
@@ -457,12 +465,16 @@ def _scaled_grads(ctx, grad_output):
     """grad * grad_output, in place (reference ops.py:804-810). The gradients already have the dtype of their
     inputs; when grad_output is exactly 1 -- a plain loss.backward() -- the kernels leave them untouched."""
     backend = get_backend()
-    dx, dW = ctx.lce_grads
+    dx, dW = ctx.lce_grads  # either may be None: the input did not require grad, so its contraction never ran
     ctx.lce_grads = None
-    factor = grad_output.detach().reshape(1).to(device=dx.device, dtype=torch.float32).contiguous()
-    backend.grad_scale_cast(dx, dx, factor)
-    backend.grad_scale_cast(dW, dW, factor)
-    return dx.view(ctx.lce_x_shape), dW
+    dev = dx.device if dx is not None else dW.device
+    factor = grad_output.detach().reshape(1).to(device=dev, dtype=torch.float32).contiguous()
+    if dx is not None:
+        backend.grad_scale_cast(dx, dx, factor)
+        dx = dx.view(ctx.lce_x_shape)
+    if dW is not None:
+        backend.grad_scale_cast(dW, dW, factor)
+    return dx, dW
 
 
 class LinearXentImplementation(torch.autograd.Function):
@@ -476,11 +488,11 @@ class LinearXentImplementation(torch.autograd.Function):
         # inside, exactly as the reference does (ops.py:665-667).
         with _device_guard(x_in):
             x, y_flat, A = _prepare(x_in, y, At)
-            want_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[2])
+            want = (bool(ctx.needs_input_grad[0]), bool(ctx.needs_input_grad[2]))
             with torch.no_grad():
                 out5, dx, dA, _ = run_pass(x, y_flat, A, ignore_index, z_regularization, logit_scale, N_chunk_size,
-                                           monitoring, want_grad)
-            ctx.lce_grads = (dx, dA) if want_grad else None
+                                           monitoring, want)
+            ctx.lce_grads = (dx, dA) if any(want) else None
             ctx.lce_x_shape = x_in.shape
             loss, z_value, logit_max, logit_ent, logit_norm = out5.unbind(0)
             ctx.mark_non_differentiable(z_value, logit_max, logit_ent, logit_norm)

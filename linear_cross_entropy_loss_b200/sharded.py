@@ -145,12 +145,12 @@ class VocabShardedLinearXent(torch.autograd.Function):
             spec = ops.ShardSpec(rank=rank, world=world, vocab_offset=rank * v_local,
                                  gather_row_parts=coll.gather_row_parts, reduce_dx=coll.reduce_dx,
                                  peer_exchange=lambda prob, dt: PeerExchange.for_problem(group, prob, dt, x.device))
-            want_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[2])
+            want = (bool(ctx.needs_input_grad[0]), bool(ctx.needs_input_grad[2]))
             with torch.no_grad():
                 out5, dx, dA, _ = ops.run_pass(x, y_flat, A, ignore_index, z_regularization, logit_scale,
-                                               N_chunk_size, monitoring, want_grad, shard=spec)
+                                               N_chunk_size, monitoring, want, shard=spec)
                 coll.wait_all()
-            ctx.lce_grads = (dx, dA) if want_grad else None
+            ctx.lce_grads = (dx, dA) if any(want) else None
             ctx.lce_x_shape = x_in.shape
             loss, z_value, logit_max, logit_ent, logit_norm = out5.unbind(0)
             ctx.mark_non_differentiable(z_value, logit_max, logit_ent, logit_norm)

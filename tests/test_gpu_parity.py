@@ -220,6 +220,28 @@ def test_forward_only_skips_the_gradient_kernels():
     assert _native.launch_count() - before > fwd_only
 
 
+def test_frozen_head_or_frozen_features_skip_one_contraction():
+    from linear_cross_entropy_loss_b200 import _native
+
+    x, y, W = random_problem(512, 256, 2048, torch.bfloat16, seed=41)
+    ref = oracle.forward_backward(x, y, W, -1)
+    xd = x.cuda().requires_grad_(True)
+    before = _native.launch_count()
+    linear_cross_entropy(xd, y.cuda(), W.cuda(), -1, 0.0, 1.0, 256)[0].backward()
+    only_dx = _native.launch_count() - before
+    assert cosine(xd.grad.double().cpu().numpy(), ref.dx) > TOL[torch.bfloat16]["cos"]
+    Wd = W.cuda().requires_grad_(True)
+    before = _native.launch_count()
+    linear_cross_entropy(x.cuda(), y.cuda(), Wd, -1, 0.0, 1.0, 256)[0].backward()
+    only_dw = _native.launch_count() - before
+    assert cosine(Wd.grad.double().cpu().numpy(), ref.dW) > TOL[torch.bfloat16]["cos"]
+    xd2 = x.cuda().requires_grad_(True)
+    before = _native.launch_count()
+    linear_cross_entropy(xd2, y.cuda(), Wd, -1, 0.0, 1.0, 256)[0].backward()
+    both = _native.launch_count() - before
+    assert only_dx < both and only_dw < both
+
+
 def test_module_forward_backward_and_metrics():
     torch.manual_seed(0)
     m = LinearCrossEntropyLoss(512, 4096, ignore_index=-1, logit_scale=0.5, z_regularization=1e-4,

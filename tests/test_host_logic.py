@@ -80,6 +80,21 @@ def test_no_gradient_work_without_requires_grad(fake):
     assert abs(out2[0].item() - out[0].item()) < 1e-7
 
 
+def test_only_the_requested_gradient_is_computed(fake):
+    """A frozen head (only x requires grad) skips the dW contraction, frozen features skip dx."""
+    x, y, W = make(seed=4)
+    want = oracle.forward_backward(x, y, W, -1)
+    xr = x.clone().requires_grad_(True)
+    linear_cross_entropy(xr, y, W, ignore_index=-1)[0].backward()
+    assert "dx_chunk" in fake.calls and "dw_chunk" not in fake.calls
+    assert np.allclose(xr.grad.numpy(), want.dx, atol=2e-7)
+    fake.calls.clear()
+    Wr = W.clone().requires_grad_(True)
+    (linear_cross_entropy(x, y, Wr, ignore_index=-1)[0] * 2).backward()
+    assert "dw_chunk" in fake.calls and "dx_chunk" not in fake.calls
+    assert np.allclose(Wr.grad.numpy(), 2 * want.dW, atol=4e-7)
+
+
 def test_leading_dimensions_are_flattened_and_grad_keeps_the_input_shape(fake):
     x, y, W = make(N=512)
     x3 = x.view(4, 128, 256).clone().requires_grad_(True)
