@@ -35,10 +35,10 @@ PUBLISHED_BF16_DEFAULT_TFLOPS = 86.75
 # fallback roofline denominators when the measured-peaks file is absent (earlier measurement on this pool)
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of each contraction kernel, from an ncu
-# capture of the quarter-size case (N=4096, H=2048, V=32768, bf16; summary kept under profiles/):
-# forward 381.9 MB, dx 931.7 MB, dW 406.5 MB. Forward and dx traffic grow in proportion to V; the figures are scaled
-# by V_local / 32768 at run time (only for N_chunk_size=4096, H=2048, which the capture used). dW is not scaled: from
-# the second chunk on it also reads and rewrites the fp32 accumulator, which the one-chunk capture does not contain.
+# capture of the quarter-size case (N=4096, H=2048, V=32768, bf16; summary kept under profiles/). Forward and dx
+# traffic grow in proportion to V; the figures are scaled by V_local / 32768 at run time (only for N_chunk_size=4096,
+# H=2048, which the capture used). dW is not scaled: from the second chunk on it also reads and rewrites the fp32
+# accumulator, which the one-chunk capture does not contain.
 NCU_DRAM_BYTES_V32768 = {"fwd": 391.4e6, "dx": 738.5e6, "dw": None}
 
 
@@ -52,10 +52,11 @@ def parse_args():
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--n-chunk-size", type=int, default=0,
                     help="override the configuration's N_chunk_size (0 = keep it; the metric's point uses 4096)")
-    ap.add_argument("--gemm-variant", type=int, default=0, choices=[0, 1, 2, 3],
-                    help="A/B measurement bits: 1 = single-CTA kernels instead of CTA pairs, 2 = dx tiles M-first")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1, rank 0)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU work of the baseline leg")
+    ap.add_argument("--triton-ref", choices=["full", "trimmed", "off"], default="full",
+                    help="N=1: also time the reference's own Triton op on this GPU (outside the timed region of the "
+                         "CUDA path) with its full autotune lists, with lists trimmed to three entries each, or not")
     ap.add_argument("--ref-budget", type=float, default=100.0,
                     help="--impl reference: seconds of CPU work over all warm-up and timed steps together")
     return ap.parse_args()
@@ -199,6 +200,28 @@ def cpu_reference_rate(cfg, seconds, steps=1, warmup=0):
     return tflops, t * 1e3, info
 
 
+def triton_reference_leg(cfg, x, y, W, mode):
+    """Times the reference's own Triton implementation (unmodified, from oracle/_ref) on the same inputs, on this GPU.
+    A baseline leg like cpu_baseline: it runs after the CUDA path's timed regions and never touches them."""
+    try:
+        import triton
+
+        from oracle import ref_triton
+
+        ref_triton.load()
+        if mode == "trimmed":
+            ref_triton.trim_configs()
+        ms, loss, chosen = ref_triton.time_fwd_bwd(
+            x.detach(), y, W.detach(), cfg.ignore_index, cfg.z_regularization, cfg.logit_scale, cfg.N_chunk_size,
+            cfg.monitoring, steps=10, warmup=3)
+        return {"tflops": cfg.flops / (ms * 1e-3) / 1e12, "ms_per_step": ms, "loss": loss,
+                "triton_version": triton.__version__, "autotune_lists": mode, "chosen_configs": chosen,
+                "note": "reference linear_cross_entropy (Triton kernels JIT-compiled for this GPU), forward+backward, "
+                        "10 steps after the autotune call and 3 warm-up calls, CUDA events"}
+    except Exception as err:  # noqa: BLE001 -- not installed, Triton cannot compile for this GPU, out of resources ...
+        return {"unavailable": f"reference Triton unavailable on this box: {type(err).__name__}: {err}"[:600]}
+
+
 def run_reference_arm(args, cfg, n_gpus):
     per_step = max(0.25, args.ref_budget / max(1, args.steps + args.warmup))
     tflops, ms, info = cpu_reference_rate(cfg, per_step, steps=args.steps, warmup=args.warmup)
@@ -225,7 +248,7 @@ def config_dict(cfg, n_gpus, args):
                         "peer stores fused into the dx contraction" if os.environ.get("LCE_PEER_DX") == "1"
                         else "NCCL all-reduce per chunk, in stream order"),
         "l2": "inputs larger than L2 (the weight alone is >= 512 MiB per GPU); no explicit flush",
-        "gemm_variant": "single-CTA 128x256 tiles" if getattr(args, "gemm_variant", 0) & 1 else "CTA-pair 256x256 tiles",
+        "gemm_variant": "CTA-pair 256x256 tiles",
     }
 
 
@@ -267,7 +290,6 @@ def main():
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    _native.check(_native.load().lce_set_gemm_variant(args.gemm_variant), "lce_set_gemm_variant")
     sharded = world > 1
     if sharded:
         dist.init_process_group("nccl", device_id=dev)
@@ -396,7 +418,7 @@ def main():
         base = NCU_DRAM_BYTES_V32768.get(dominant)
         traffic = (base * v_local / 32768.0) if (base and cfg.H == 2048 and min(cfg.N, cfg.N_chunk_size) == 4096) \
             else None
-        roofline = {"bound": "tensor", "kernel": ("lce_gemm_kernel" if getattr(args, "gemm_variant", 0) & 1 else "lce_gemm_pair_kernel") + f"[{dominant}]", "achieved": achieved,
+        roofline = {"bound": "tensor", "kernel": f"lce_gemm_pair_kernel[{dominant}]", "achieved": achieved,
                     "peak": peak_tflops, "unit": "TFLOP/s", "frac": achieved / peak_tflops,
                     "peak_source": f"{peak_source} cuBLAS bf16 GEMM, sustained",
                     "traffic": traffic,
@@ -415,8 +437,13 @@ def main():
                 "d2h_bytes_per_step": 4},
         "gpu_launches": launches, "roofline": roofline, "loss": loss_value,
         "peak_extra_bytes": peak_extra, "peak_budget_bytes": min(cfg.N, cfg.N_chunk_size) * v_local * 4,
+        # the same without the gradients the caller receives and the fp32 dW accumulator (which the reference keeps too)
+        "peak_extra_bytes_excl_grads": peak_extra - cfg.N * cfg.H * x.element_size()
+        - cfg.H * v_local * (4 if cfg.N > cfg.N_chunk_size else W.element_size()),
     }
 
+    if rank == 0 and world == 1 and args.triton_ref != "off":
+        line["triton_reference"] = triton_reference_leg(cfg, x, y, W, args.triton_ref)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         _, _, info = cpu_reference_rate(cfg, args.cpu_seconds)
         line["cpu_baseline"] = info

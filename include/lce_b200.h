@@ -139,6 +139,12 @@ int lce_combine_chunk(const lce_problem* p, const float* row_parts_all, const in
  *                the pass: the finished sum is written there in the element type of x / W (row stride
  *                dwf_ld) and dweight_acc is only read. A pass of a single call (first != 0 and dweight_final
  *                given) needs no dweight_acc at all (may be null).
+ *                dweight_final == dweight_acc (the same address) asks for the finished sum to be written OVER the
+ *                accumulator, which saves the separate hidden x vocab output buffer while the workspace is still
+ *                alive: element (r, j) of the result, in the element type of W (es bytes), then lies at byte
+ *                4 * dw_ld * r + 1024 * (j / 256) + es * (j % 256) of dweight_acc, i.e. every 256-column tile keeps
+ *                its place and is narrowed inside its own 1024 bytes (a strided view for the caller to compact
+ *                after it has released the workspace). dwf_ld is ignored; for fp32 the accumulator is the result.
  * lce_backward_chunk = the three in sequence. */
 int lce_dz_chunk(const lce_problem* p, const void* x, int64_t x_ld, const int64_t* labels, int64_t row0,
                  int64_t rows, void* workspace, void* stream);
@@ -224,7 +230,7 @@ int lce_read_status(void* workspace, void* stream);
  *   - p: n_rows_total, hidden, vocab_local, dtype, ignore_index, logit_scale, z_regularization and
  *     monitoring are used; chunk_rows, world, vocab_offset and want_grad are ignored (forward only,
  *     unsharded; rows are processed in the largest chunks whose statistics fit the scratch).
- *   - LCE_ERR_TOO_LARGE if not even 128 rows fit (vocab_local beyond about 2 million columns); the other
+ *   - LCE_ERR_TOO_LARGE if not even 128 rows fit (vocab_local beyond about 2 million columns without monitoring, 1 million with); the other
  *     shape rules are those of lce_forward_chunk.
  *   - The first call on each device resolves the scratch array's device address (cudaGetSymbolAddress) and
  *     sets kernel attributes; make that first call outside of any stream capture.
@@ -246,21 +252,19 @@ int lce_profile_enable(int32_t enable);
 int lce_profile_read(double* ms3, long long* launches3);
 
 /* ---- diagnostics ------------------------------------------------------------------------------
- * lce_set_gemm_variant: bit mask, 0 by default. Bit 0 forces the single-CTA kernel (128 x 256 tiles) everywhere
- * instead of CTA pairs (cta_group::2, 256 x 256 tiles); bit 1 makes the dx contraction walk its tiles M-first
- * instead of N-first. Process-wide; for A/B measurements and tests. No counterpart in the reference. */
-int lce_set_gemm_variant(int32_t variant);
-
-/*
+ * Not part of the pass: stateless, changes nothing the other entry points see.
+ *
  * Runs the GEMM engine alone: out[s][M, N] = A * B^T over K-split s (fp32, row stride N).
  * a_mn_major == 0: a is [M, K] (K contiguous, row stride a_ld); != 0: a is [K, M] (row stride a_ld).
  * Same for b with N. M % 128 == 0, N % 256 == 0, K % (splits * 128 bytes) == 0.
+ * single_cta != 0: use the single-CTA kernel (128 x 256 tiles) even where the pass would use CTA pairs
+ * (cta_group::2, 256 x 256 tiles; the pass falls back to the single-CTA kernel for an odd number of 128-row tiles).
  * dev_status: int[8] device words, 8-byte aligned: [0] status (0 = ok); [2..3] int64 SM cycles and [4..5] int64
  * nanoseconds that CTA 0 spent in the kernel (their ratio is the SM clock the kernel ran at).
  * No counterpart in the reference. */
 int lce_debug_gemm(int32_t dtype, int32_t a_mn_major, int32_t b_mn_major, const void* a, int64_t a_ld,
                    const void* b, int64_t b_ld, float* out, int64_t m, int64_t n, int64_t k, int32_t splits,
-                   int* dev_status, void* stream);
+                   int32_t single_cta, int* dev_status, void* stream);
 
 #ifdef __cplusplus
 }

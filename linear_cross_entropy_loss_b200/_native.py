@@ -73,10 +73,25 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     """Compile the CUDA sources for sm_100a into ``liblce_b200.so`` next to this file."""
     if not force and not needs_build():
         return LIB_PATH
+    # One build at a time across PROCESSES too: under torchrun every rank may find the library stale at once.
+    # The file lock serialises them; whoever gets it second finds the library fresh and returns.
+    import fcntl
+
+    with open(_PKG_DIR / ".build.lock", "w") as lock_file:
+        fcntl.flock(lock_file, fcntl.LOCK_EX)
+        try:
+            if not force and not needs_build():
+                return LIB_PATH
+            return _build_locked(verbose)
+        finally:
+            fcntl.flock(lock_file, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose: bool) -> Path:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: liblce_b200.so cannot be built")
-    tmp = LIB_PATH.with_suffix(".so.tmp")
+    tmp = LIB_PATH.parent / f"{LIB_PATH.name}.{os.getpid()}.tmp"
     cmd = [
         nvcc,
         "-gencode", "arch=compute_100a,code=sm_100a",
@@ -142,12 +157,11 @@ SIGNATURES = {
     "lce_read_status": (ctypes.c_int, [_vp, _vp]),
     "lce_rerun_stats_async": (ctypes.c_int, [_vp, _vp, _vp]),
     "lce_eval_loss_static": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _vp, _vp, _vp]),
-    "lce_set_gemm_variant": (ctypes.c_int, [_i32]),
     "lce_profile_enable": (ctypes.c_int, [_i32]),
     "lce_profile_read": (ctypes.c_int, [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]),
     "lce_debug_gemm": (
         ctypes.c_int,
-        [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _vp, _vp],
+        [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _vp],
     ),
 }
 

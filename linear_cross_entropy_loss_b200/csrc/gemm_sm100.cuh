@@ -77,12 +77,17 @@ struct GemmParams {
   const float* out_div;
   void* out_final;             // when non-null the result goes here, converted to the input element type,
   long long out_final_ld;      // instead of back to `out` (last accumulation step of dW)
+  int out_final_inplace;       // 1: the converted result overwrites the accumulator itself: element (r, j) goes to
+                               // byte 4 * out_ld * r + 1024 * (j / 256) + es * (j % 256) of `out` -- the first
+                               // half (16-bit types) of the tile's own row segment, so a thread only overwrites
+                               // accumulator values that it has read before (out_final is ignored)
   int out_rows;                // rows / columns of the output that exist; tiles may hang over both edges
   int out_cols;
   int out_vector_ok;           // 1: out, out_final and their strides allow 32-byte accesses
 
   // ---- EPI_FWD: softmax statistics + exp slab
-  void* slab;                  // [rows, slab_ld] in the input element type: exp(z - tile row max)
+  void* slab;                  // [rows, slab_ld] in the input element type: exp(z - b) with b = the row's reference
+                               // (row-reference mode) or the maximum of the (row, tile) (per-tile mode)
   long long slab_ld;
   int store_slab;              // 0 when no gradient is wanted
   float* tile_max;             // [n_tiles, stat_ld] per (V tile, row): max_j z
@@ -394,7 +399,10 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr
   } else {
     dst = p.out + (long long)split * p.out_split_stride + row * p.out_ld + (long long)n_blk * BLOCK_N;
   }
-  Elem* dst_final = reinterpret_cast<Elem*>(p.out_final) + row * p.out_final_ld + (long long)n_blk * BLOCK_N;
+  Elem* dst_final = p.out_final_inplace
+                        ? reinterpret_cast<Elem*>(dst)
+                        : reinterpret_cast<Elem*>(p.out_final) + row * p.out_final_ld + (long long)n_blk * BLOCK_N;
+  const bool to_final = p.out_final_inplace || p.out_final != nullptr;
   float coef = (p.out_div != nullptr) ? p.out_scale / __ldg(p.out_div) : p.out_scale;
   if (p.row_coef != nullptr) coef *= p.row_coef[row];  // row_coef covers the padded rows too
 #pragma unroll 1
@@ -456,7 +464,7 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr
 #pragma unroll
         for (int i = 0; i < 32; ++i) r[i] = coef * __uint_as_float(v[i]);
       }
-      if (p.out_final != nullptr)
+      if (to_final)
         store_slab_chunk(dst_final + c * 32, r);
       else
         store_slab_chunk(dst + c * 32, r);
@@ -467,7 +475,7 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr
         if (i < lim) {
           float val = coef * __uint_as_float(v[i]);
           if (p.accumulate) val += dst[c * 32 + i];
-          if (p.out_final != nullptr)
+          if (to_final)
             dst_final[c * 32 + i] = cast_elem<Elem>(val);
           else
             dst[c * 32 + i] = val;

@@ -19,9 +19,6 @@ namespace {
 using namespace lce;
 
 std::atomic<long long> g_launches{0};
-// bit 0: always the single-CTA kernel instead of the CTA-pair kernel; bit 1: dx walks its tiles M-first like the
-// other two contractions instead of N-first (lce_set_gemm_variant; both bits are for A/B measurements)
-std::atomic<int> g_gemm_variant{0};
 
 // ------------------------------------------------------------------------------------------------
 // device bookkeeping
@@ -289,9 +286,7 @@ struct ProfScope {
 // With an even number of 128-row tiles (and at least two SMs) a contraction runs on the CTA-pair kernel:
 // 256 x 256 tiles, one per cluster of two CTAs, each CTA loading 128 rows of A and 128 of the 256 B columns.
 // The B tensor map must be built for the variant that will run (rows_of_b_tile).
-bool use_pair_kernel(long long m_tiles128, int sms) {
-  return (m_tiles128 % 2 == 0) && sms >= 2 && (g_gemm_variant.load(std::memory_order_relaxed) & 1) == 0;
-}
+bool use_pair_kernel(long long m_tiles128, int sms) { return (m_tiles128 % 2 == 0) && sms >= 2; }
 int rows_of_b_tile(bool pair) { return pair ? BLOCK_N / 2 : BLOCK_N; }
 
 // gp.m_tiles counts 128-row tiles; `pair` must be the value the tensor maps were built for.
@@ -358,8 +353,7 @@ const char* lce_status_string(int status) {
     case LCE_OK: return "ok";
     case LCE_ERR_INVALID_ARGUMENT: return "invalid argument";
     case LCE_ERR_UNSUPPORTED_SHAPE:
-      return "unsupported shape (chunk rows % 128, hidden % 8 and vocab % 8 must be 0; calls start on 128-row "
-             "boundaries)";
+      return "unsupported shape (chunk rows % 128 and hidden % 8 must be 0; calls start on 128-row boundaries)";
     case LCE_ERR_MISALIGNED: return "pointer or row stride not 16-byte aligned";
     case LCE_ERR_UNSUPPORTED_DEVICE: return "device is not compute capability 10.x (sm_100a required)";
     case LCE_ERR_CUDA: return "CUDA runtime error";
@@ -645,7 +639,7 @@ int launch_dx_gemm(const lce_problem* p, const void* weight, int64_t w_ld, int64
   gp.a_mn0 = (int)local0;
   // N-first: the units in flight at one time then cover all H tiles of a few row blocks, so each slab row block is
   // streamed from DRAM once and only the (smaller) weight is re-read per group of row blocks
-  gp.n_fastest = (g_gemm_variant.load(std::memory_order_relaxed) & 2) ? 0 : 1;
+  gp.n_fastest = 1;
   gp.out = w.dx_part + local0 * h_pad;  // padded partial buffer: whole tiles are stored, the reduction reads what exists
   gp.out_ld = h_pad;
   gp.out_split_stride = (long long)p->chunk_rows * h_pad;
@@ -746,7 +740,7 @@ int lce_dx_chunk_peer(const lce_problem* p, const void* weight, int64_t w_ld, in
   sc.rank = peers->rank;
   sc.buf = (int)(epoch & 1u);
   if ((v = launch_dx_gemm(p, weight, w_ld, row0, rows, w, sms, st, &sc)) != LCE_OK) return v;
-  peer_signal_kernel<<<1, 32, 0, st>>>(sc.bases, sc.world, sc.rank, 0, epoch);
+  peer_signal_kernel<<<1, 32, 0, st>>>(sc.bases, sc.world, sc.rank, 0, epoch, nullptr);
   return check_launch();
 }
 
@@ -796,7 +790,8 @@ int lce_dx_reduce_peer(const lce_problem* p, int64_t row0, int64_t rows, void* w
                                                            (int)p->hidden, l.stage_off(buf), &w.scalars->status);
   }
   if ((v = check_launch()) != LCE_OK) return v;
-  peer_signal_kernel<<<1, 32, 0, st>>>(bases, peers->world, rank, 1, epoch);
+  // not published when the wait above ran out (status word set): nothing was staged, so nobody may copy
+  peer_signal_kernel<<<1, 32, 0, st>>>(bases, peers->world, rank, 1, epoch, &w.scalars->status);
   return check_launch();
 }
 
@@ -853,9 +848,11 @@ int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0
   if (!p->want_grad || !x || !workspace) return LCE_ERR_INVALID_ARGUMENT;
   if (x_ld < p->hidden) return LCE_ERR_INVALID_ARGUMENT;
   // the fp32 accumulator is needed unless this single call both starts and finishes the accumulation
-  const bool need_acc = !(first && dweight_final != nullptr);
+  // dweight_final == dweight_acc: the finished sum overwrites the accumulator in W's element type (tile-gapped layout)
+  const bool inplace = dweight_final != nullptr && dweight_final == static_cast<void*>(dweight_acc);
+  const bool need_acc = !(first && dweight_final != nullptr) || inplace;
   if (need_acc && (!dweight_acc || dw_ld < p->vocab_local)) return LCE_ERR_INVALID_ARGUMENT;
-  if (dweight_final && dwf_ld < p->vocab_local) return LCE_ERR_INVALID_ARGUMENT;
+  if (dweight_final && !inplace && dwf_ld < p->vocab_local) return LCE_ERR_INVALID_ARGUMENT;
   if (dweight_acc && (reinterpret_cast<uintptr_t>(dweight_acc) & 3u) != 0) return LCE_ERR_MISALIGNED;
   if (dweight_final && (reinterpret_cast<uintptr_t>(dweight_final) & (uintptr_t)(elem_size(p->dtype) - 1)) != 0)
     return LCE_ERR_MISALIGNED;
@@ -891,7 +888,8 @@ int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0
   gp.k_blocks = (int)(rows_pad * es / 128);
   gp.out_rows = (int)p->hidden;
   gp.out_cols = (int)p->vocab_local;
-  gp.out_vector_ok = (rows_aligned32(dweight_acc, dw_ld * 4) && rows_aligned32(dweight_final, dwf_ld * es)) ? 1 : 0;
+  gp.out_vector_ok =
+      (rows_aligned32(dweight_acc, dw_ld * 4) && (inplace || rows_aligned32(dweight_final, dwf_ld * es))) ? 1 : 0;
   gp.a_k0 = (int)(rowref ? local0 : row0);
   gp.b_k0 = (int)local0;
   gp.out = dweight_acc;
@@ -900,8 +898,9 @@ int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0
   gp.accumulate = first ? 0 : 1;
   gp.out_scale = p->logit_scale;
   gp.out_div = &w.scalars->n_valid;
-  gp.out_final = dweight_final;
+  gp.out_final = inplace ? nullptr : dweight_final;
   gp.out_final_ld = dwf_ld;
+  gp.out_final_inplace = (inplace && p->dtype != LCE_DTYPE_F32) ? 1 : 0;  // fp32: the accumulator IS the result
   gp.status = &w.scalars->status;
   {
     ProfScope prof(PROF_DW, st);
@@ -1005,12 +1004,6 @@ int lce_rerun_stats_async(void* workspace, int32_t* host_out2, void* stream) {
   return LCE_OK;
 }
 
-int lce_set_gemm_variant(int32_t variant) {
-  if (variant < 0 || variant > 3) return LCE_ERR_INVALID_ARGUMENT;
-  g_gemm_variant.store(variant, std::memory_order_relaxed);
-  return LCE_OK;
-}
-
 int lce_profile_enable(int32_t enable) {
   std::lock_guard<std::mutex> lock(g_prof_mutex);
   g_prof_enabled = enable != 0;
@@ -1040,8 +1033,8 @@ int lce_profile_read(double* ms3, long long* launches3) {
 }
 
 int lce_debug_gemm(int32_t dtype, int32_t a_mn_major, int32_t b_mn_major, const void* a, int64_t a_ld, const void* b,
-                   int64_t b_ld, float* out, int64_t m, int64_t n, int64_t k, int32_t splits, int* dev_status,
-                   void* stream) {
+                   int64_t b_ld, float* out, int64_t m, int64_t n, int64_t k, int32_t splits, int32_t single_cta,
+                   int* dev_status, void* stream) {
   if (dtype != LCE_DTYPE_F16 && dtype != LCE_DTYPE_BF16 && dtype != LCE_DTYPE_F32) return LCE_ERR_INVALID_ARGUMENT;
   if (!a || !b || !out || !dev_status || m <= 0 || n <= 0 || k <= 0 || splits < 1) return LCE_ERR_INVALID_ARGUMENT;
   const int es = elem_size(dtype);
@@ -1051,7 +1044,7 @@ int lce_debug_gemm(int32_t dtype, int32_t a_mn_major, int32_t b_mn_major, const 
   int sms = 0;
   int v = ensure_device(&sms);
   if (v != LCE_OK) return v;
-  const bool pair = use_pair_kernel(m / BLOCK_M, sms);
+  const bool pair = !single_cta && use_pair_kernel(m / BLOCK_M, sms);
   CUtensorMap ta, tb;
   v = a_mn_major ? make_operand_tmap(&ta, dtype, true, a, m, k, a_ld, BLOCK_M)
                  : make_operand_tmap(&ta, dtype, false, a, k, m, a_ld, BLOCK_M);
@@ -1134,6 +1127,8 @@ extern "C" int lce_eval_loss_static(const lce_problem* p_in, const void* x, int6
     best = rows;
   }
   if (best == 0) return LCE_ERR_TOO_LARGE;  // even 128 rows of statistics exceed the fixed scratch: vocab too large
+  // whole 256-row tiles when at least one fits: an even number of 128-row tiles runs on the CTA-pair kernel
+  if (best >= 2 * BLOCK_M) best -= best % (2 * BLOCK_M);
   p.chunk_rows = best;
 
   void* scratch = nullptr;

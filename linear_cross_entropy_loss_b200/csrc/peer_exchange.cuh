@@ -59,6 +59,11 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ float4 ld_global_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ unsigned long long wall_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -68,8 +73,13 @@ __device__ __forceinline__ unsigned long long wall_ns() {
 // flag[phase][rank] = epoch in every rank's buffer. Launched after the kernel whose stores it publishes:
 // the kernel boundary orders those stores before this thread, the system-scope fence and release before
 // the flag.
-__global__ void peer_signal_kernel(PeerBases peers, int world, int rank, int phase, uint32_t epoch) {
+// skip_if: when non-null and *skip_if != 0 (the pass's status word after a wait of the preceding kernel ran
+// out, so that kernel wrote nothing) the flag is NOT published: the other ranks' waits then run out too and
+// they report the failure instead of copying rows that were never written.
+__global__ void peer_signal_kernel(PeerBases peers, int world, int rank, int phase, uint32_t epoch,
+                                   const int* skip_if) {
   const int t = threadIdx.x;
+  if (skip_if != nullptr && *skip_if != 0) return;
   if (t < world) {
     __threadfence_system();
     st_release_sys(reinterpret_cast<uint32_t*>(peers.base[t]) + phase * kMaxPeers + rank, epoch);
@@ -131,7 +141,7 @@ struct Pack8<__nv_bfloat16> {
 // (indices local to the owned slice); chunk_row0 = chunk-local index of owned row 0.
 template <typename T>
 __global__ void peer_reduce_push_kernel(PeerBases peers, int world, const uint32_t* flags_a, uint32_t epoch,
-                                        long long limit_ns, const float* __restrict__ recv, int slots, int rows_own,
+                                        long long limit_ns, const float* recv, int slots, int rows_own,
                                         int ld, int own_lo, int own_hi, int chunk_row0, int hidden,
                                         size_t stage_off, int* status) {
   if (!peer_wait_all(flags_a, world, epoch, limit_ns, status)) return;
@@ -147,8 +157,10 @@ __global__ void peer_reduce_push_kernel(PeerBases peers, int world, const uint32
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] = 0.f;
     for (int s = 0; s < slots; ++s) {
-      const float4 a = *reinterpret_cast<const float4*>(src + s * slot_stride);
-      const float4 b = *reinterpret_cast<const float4*>(src + s * slot_stride + 4);
+      // recv was written by other GPUs while this kernel may already have been running: plain coherent loads
+      // (never the read-only path, which is only defined for data that no one writes during the kernel)
+      const float4 a = ld_global_f4(src + s * slot_stride);
+      const float4 b = ld_global_f4(src + s * slot_stride + 4);
       acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w;
       acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
     }
@@ -160,7 +172,7 @@ __global__ void peer_reduce_push_kernel(PeerBases peers, int world, const uint32
 // Step 3: copy rows [row_lo, row_lo + rows) (chunk-local) of this rank's stage buffer into dx.
 template <typename T>
 __global__ void peer_finish_kernel(const uint32_t* flags_b, int world, uint32_t epoch, long long limit_ns,
-                                   const T* __restrict__ stage, int row_lo, int rows, int hidden, T* __restrict__ dx_rows,
+                                   const T* stage, int row_lo, int rows, int hidden, T* __restrict__ dx_rows,
                                    long long dx_ld, int* status) {
   if (!peer_wait_all(flags_b, world, epoch, limit_ns, status)) return;
   const int octs = hidden >> 3;
@@ -174,7 +186,7 @@ __global__ void peer_finish_kernel(const uint32_t* flags_b, int world, uint32_t 
     T* dst = dx_rows + (long long)r * dx_ld + c;
 #pragma unroll
     for (int v = 0; v < 8 / kVec; ++v)
-      reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<const uint4*>(src)[v];
+      reinterpret_cast<float4*>(dst)[v] = ld_global_f4(reinterpret_cast<const float*>(src) + 4 * v);
   }
 }
 

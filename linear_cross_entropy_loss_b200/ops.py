@@ -212,13 +212,23 @@ def _side_stream(device: torch.device, role: str = "slab"):
     return _side_streams[key]
 
 
-def _split_rows(row0: int, rows: int, per_tile: bool):
+def _split_rows(row0: int, rows: int, split: bool):
     """Sub-chunks of a chunk: halves when each half keeps the 256-row granularity of the CTA-pair kernels.
     Only the per-tile slab mode has a slab-wide transform worth hiding; the default mode of bf16 / fp32 runs a
     chunk as one piece."""
-    if per_tile and SUBCHUNKS == 2 and rows >= 1024 and rows % 512 == 0:
+    if split and SUBCHUNKS == 2 and rows >= 1024 and rows % 512 == 0:
         return [(row0, rows // 2), (row0 + rows // 2, rows // 2)]
     return [(row0, rows)]
+
+
+def _wants_subchunks(per_tile: bool, want_grad: bool, dtype, sharded: bool) -> bool:
+    """Whether chunks are processed as two halves. Every half issues its own collectives in a sharded run, so there
+    the answer may only depend on values that are equal on all ranks: the slab mode is not one of them (each rank
+    picks it from its own re-run counters and a polled event), the dtype is. The row partials a rank exports are
+    the same in both modes (base, sums), so ranks in different modes still combine correctly."""
+    if not want_grad:
+        return False
+    return dtype == torch.float16 if sharded else per_tile
 
 
 class SlabModePolicy:
@@ -286,12 +296,13 @@ slab_mode_policy = SlabModePolicy()
 
 
 def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size, monitoring, want_grad,
-             shard: Optional[ShardSpec] = None):
+             shard: Optional[ShardSpec] = None, keep_workspace: bool = False):
     """One forward(+gradient) pass over all row chunks.
 
     x: (N, H) with unit inner stride, y: (N,) int64 contiguous, At: (H, V_local) with unit inner stride.
     Returns (out5, dx, dW, workspace): out5 = float32[5] (loss, z_value, logit_max, logit_entropy,
-    logit_norm); dx (N, H) and dW (H, V_local) in the dtype of x / At, or None without want_grad.
+    logit_norm); dx (N, H) and dW (H, V_local) in the dtype of x / At, or None without want_grad; the workspace
+    only with ``keep_workspace`` (tests read the device status word from it), else None.
     Follows the chunk loop of the reference (ops.py:721-791): per chunk forward, [all-gather of the row
     partials,] log-sum-exp combine, dZ preparation, dx, dW accumulation. For fp16 -- whose dZ preparation is a
     pass over the whole slab -- a chunk runs as two sub-chunks and the combine + slab pass of one sub-chunk go
@@ -321,9 +332,9 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
 
     world = 1 if shard is None else shard.world
     policy_key = (x.device.index, x.dtype, H, V, N_group, world)
-    slab_mode = slab_mode_policy.choose(policy_key, x.dtype) if native else (
-        _native.SLAB_PER_TILE if x.dtype == torch.float16 else _native.SLAB_DEFAULT)
+    slab_mode = slab_mode_policy.choose(policy_key, x.dtype)
     per_tile = slab_mode == _native.SLAB_PER_TILE
+    split = _wants_subchunks(per_tile, want_grad, x.dtype, shard is not None)
     prob = Problem(
         n_rows_total=N, chunk_rows=N_group, hidden=H, vocab_local=V,
         vocab_offset=0 if shard is None else shard.vocab_offset, ignore_index=int(ignore_index), world=world,
@@ -339,12 +350,16 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     if want_dx:
         dx = torch.empty((N, H), dtype=x.dtype, device=dev)
     if want_dW:
-        dW = _aligned_rows_like((H, V), At.dtype, dev)
-        if n_chunks > 1:  # fp32 accumulator across chunks; the last chunk writes dW from it
+        if n_chunks > 1:
+            # fp32 accumulator across chunks. The last chunk narrows it IN PLACE to W's element type (every 256-column
+            # tile inside its own bytes), so that no second (H, V) buffer is alive together with the workspace; the
+            # narrowed tiles are compacted into dW once the workspace has been released (see the end of the pass).
             dW_acc = _aligned_rows_like((H, V), torch.float32, dev)
+        else:
+            dW = _aligned_rows_like((H, V), At.dtype, dev)
 
     # second stream only where sub-chunks exist (per-tile slabs); everything else runs in order on the caller's stream
-    use_side = native and dev.type == "cuda" and per_tile and want_grad and SUBCHUNKS == 2
+    use_side = native and dev.type == "cuda" and split and SUBCHUNKS == 2
     main = torch.cuda.current_stream(dev) if use_side else None
     side = _side_stream(dev) if use_side else None
 
@@ -366,7 +381,7 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     backend.begin(prob, y, workspace)
     for ci, row0 in enumerate(range(0, N, N_group)):
         rows = min(N_group, N - row0)
-        subs = _split_rows(row0, rows, per_tile and want_grad)
+        subs = _split_rows(row0, rows, split)
         ready = []
         for r0, n in subs:
             backend.forward_chunk(prob, x, At, y, r0, n, workspace, row_parts)
@@ -418,7 +433,8 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
                     shard.reduce_dx(dx[r0:r0 + n])
             last = ci == n_chunks - 1
             if want_dW:
-                backend.dw_chunk(prob, x, row0, rows, workspace, dW_acc, ci == 0, dW if last else None)
+                final = None if not last else (dW if dW_acc is None else dW_acc)
+                backend.dw_chunk(prob, x, row0, rows, workspace, dW_acc, ci == 0, final)
     if side is not None:
         main.wait_stream(side)
     if xstream is not None:
@@ -426,7 +442,45 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     backend.finalize(prob, workspace, out5)
     if native and not per_tile and x.dtype != torch.float16 and os.environ.get("LCE_SLAB_MODE", "auto") == "auto":
         slab_mode_policy.record(policy_key, backend, workspace)
-    return out5, dx, dW, workspace
+    if dW_acc is not None:
+        if not keep_workspace:
+            workspace = None  # released before dW is allocated: stream order makes the reuse of its memory safe
+        dW = _compact_narrowed(dW_acc, At.dtype, V)
+    return out5, dx, dW, (workspace if keep_workspace else None)
+
+
+def _narrowed_tiles(acc: torch.Tensor, dtype, V: int):
+    """Views of an fp32 accumulator (H, V) whose last chunk was narrowed in place (``lce_dw_chunk`` with
+    dweight_final == dweight_acc): [(view of the narrowed values, first column, end column), ...]. Each 256-column
+    tile keeps its 1024 bytes per row and holds its values, in ``dtype``, at the start of them."""
+    H = acc.shape[0]
+    base = acc if acc.is_contiguous() else acc._base  # rows padded to 8 columns: the tiles live in the padded buffer
+    per = 4 // dtype.itemsize  # narrow elements per fp32 slot
+    narrow = base.view(dtype)  # (H, per * ld)
+    full = V // 256
+    out = []
+    if full:
+        tiles = narrow[:, :full * 256 * per].view(H, full, 256 * per)[:, :, :256]
+        out.append((tiles, 0, full * 256))
+    if V % 256:
+        out.append((narrow[:, full * 256 * per:full * 256 * per + V % 256], full * 256, V))
+    return out
+
+
+def _compact_narrowed(acc: torch.Tensor, dtype, V: int) -> torch.Tensor:
+    """dW (H, V) in ``dtype`` from the accumulator the last chunk narrowed in place; for fp32 the accumulator itself."""
+    if dtype == torch.float32:
+        return acc
+    H = acc.shape[0]
+    dW = _aligned_rows_like((H, V), dtype, acc.device)
+    for tiles, c0, c1 in _narrowed_tiles(acc, dtype, V):
+        dst = dW[:, c0:c1]
+        if tiles.dim() == 3:
+            base = dW if dW.is_contiguous() else dW._base
+            base[:, :c1].view(H, tiles.shape[1], 256).copy_(tiles)
+        else:
+            dst.copy_(tiles)
+    return dW
 
 
 def _device_guard(t: torch.Tensor):

@@ -99,7 +99,18 @@ class FakeBackend:
         assert dz.shape[0] == rows
         g = torch.from_numpy(x[row0:row0 + rows].double().numpy().T @ dz * coef).float()
         total = g if first else dW_acc + g
-        if dW_final is not None:
+        if dW_final is not None and dW_acc is not None and dW_final.data_ptr() == dW_acc.data_ptr():
+            # the finished sum overwrites the accumulator, narrowed tile by tile (see lce_dw_chunk)
+            dtype = {0: torch.float16, 1: torch.bfloat16, 2: torch.float32}[prob.dtype]
+            if dtype == torch.float32:
+                dW_acc.copy_(total)
+            else:
+                from linear_cross_entropy_loss_b200 import ops
+
+                for tiles, c0, c1 in ops._narrowed_tiles(dW_acc, dtype, total.shape[1]):
+                    src = total[:, c0:c1].to(dtype)
+                    tiles.copy_(src.view(src.shape[0], -1, 256) if tiles.dim() == 3 else src)
+        elif dW_final is not None:
             dW_final.copy_(total.to(dW_final.dtype))
         else:
             dW_acc.copy_(total)

@@ -10,13 +10,16 @@ pytestmark = pytest.mark.gpu
 CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
 
 
+SINGLE_CTA = 0
+
+
 @pytest.fixture(params=[0, 1], ids=["cta_pair", "single_cta"], autouse=True)
 def gemm_variant(request):
     """Every test of this file runs once per kernel variant (pair kernels need M % 256 == 0, else fall back)."""
-    lib = _native.load()
-    assert lib.lce_set_gemm_variant(request.param) == 0
+    global SINGLE_CTA
+    SINGLE_CTA = request.param
     yield request.param
-    assert lib.lce_set_gemm_variant(0) == 0
+    SINGLE_CTA = 0
 
 
 def run(dtype, a_mn, b_mn, M, N, K, splits=1, seed=0):
@@ -30,7 +33,7 @@ def run(dtype, a_mn, b_mn, M, N, K, splits=1, seed=0):
     out = torch.full((splits, M, N), float("nan"), dtype=torch.float32, device="cuda")
     status = torch.zeros(8, dtype=torch.int32, device="cuda")
     rc = lib.lce_debug_gemm(CODE[dtype], a_mn, b_mn, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
-                            out.data_ptr(), M, N, K, splits, status.data_ptr(),
+                            out.data_ptr(), M, N, K, splits, SINGLE_CTA, status.data_ptr(),
                             torch.cuda.current_stream().cuda_stream)
     assert rc == 0, _native.status_string(rc)
     torch.cuda.synchronize()
@@ -65,7 +68,7 @@ def test_shape_errors_are_status_codes():
     o = torch.zeros(256, 256, dtype=torch.float32, device="cuda")
     s = torch.zeros(8, dtype=torch.int32, device="cuda")
     call = lambda m, n, k, sp=1: lib.lce_debug_gemm(1, 0, 0, t.data_ptr(), 256, t.data_ptr(), 256, o.data_ptr(), m, n,
-                                                    k, sp, s.data_ptr(), None)
+                                                    k, sp, SINGLE_CTA, s.data_ptr(), None)
     assert call(100, 256, 256) == -2
     assert call(128, 100, 256) == -2
     assert call(128, 256, 100) == -2

@@ -382,5 +382,5 @@ def test_randomised_shapes_options_and_modes(seed, monkeypatch):
 def test_device_status_is_clean_after_a_pass():
     from linear_cross_entropy_loss_b200 import ops
     x, y, W = random_problem(256, 256, 512, torch.bfloat16, seed=15)
-    out5, dx, dA, ws = ops.run_pass(x.cuda(), y.cuda(), W.cuda(), -1, 0.0, 1.0, 128, False, True)
+    out5, dx, dA, ws = ops.run_pass(x.cuda(), y.cuda(), W.cuda(), -1, 0.0, 1.0, 128, False, True, keep_workspace=True)
     assert ops.get_backend().read_status(ws) == 0

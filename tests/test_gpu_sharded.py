@@ -151,6 +151,49 @@ def test_peer_wait_runs_out_and_reports_instead_of_hanging():
     assert torch.isnan(out5[0])
 
 
+def test_a_rank_whose_wait_ran_out_publishes_nothing_so_its_peers_report_too():
+    """Two emulated ranks. Rank 0 never runs its dx contraction, so the owner step of rank 0 runs out of time. It must
+    then NOT publish its "rows are staged" flag: rank 1, whose own owner step succeeded, has to run out in its copy
+    step as well -- status set, dx untouched -- instead of copying rows that rank 0 never staged. Every wait is
+    bounded (200 ms); nothing faults."""
+    be = ops.get_backend()
+    world, N, H, V, dtype = 2, 256, 256, 1024, torch.bfloat16
+    x, y, W = random_problem(N, H, V, dtype, seed=5)
+    xd, yd = x.cuda(), y.cuda()
+    vl = V // world
+    slabs = [W[:, g * vl:(g + 1) * vl].contiguous().cuda() for g in range(world)]
+    probs = [_native.Problem(n_rows_total=N, chunk_rows=256, hidden=H, vocab_local=vl, vocab_offset=g * vl,
+                             ignore_index=-1, world=world, dtype=_native.DTYPE_BF16, monitoring=0, want_grad=1,
+                             logit_scale=1.0, z_regularization=0.0) for g in range(world)]
+    ws = [torch.empty(be.workspace_bytes(p), dtype=torch.uint8, device="cuda") for p in probs]
+    bufs = [torch.zeros(be.peer_bytes(probs[0], dtype), dtype=torch.uint8, device="cuda") for _ in range(world)]
+    tables = []
+    for g in range(world):
+        t = _native.PeerTable()
+        t.world, t.rank = world, g
+        for k in range(world):
+            t.base[k] = bufs[k].data_ptr()
+        tables.append(t)
+    parts = torch.empty(world, 6 * 256, dtype=torch.float32, device="cuda")
+    dx = [torch.full((N, H), 7.0, dtype=dtype, device="cuda") for _ in range(world)]
+    for g in range(world):
+        be.begin(probs[g], yd, ws[g])
+        be.forward_chunk(probs[g], xd, slabs[g], yd, 0, N, ws[g], parts[g])
+    for g in range(world):
+        be.combine_chunk(probs[g], parts, yd, 0, N, ws[g])
+        be.dz_chunk(probs[g], xd, yd, 0, N, ws[g])
+    be.dx_chunk_peer(probs[1], slabs[1], 0, N, ws[1], tables[1], dtype, 1)   # rank 1 scatters and signals; rank 0 never does
+    bufs[1][:1024].view(torch.int32)[0] = 1   # as if rank 0's "tiles sent" flag had reached rank 1 only
+    for g in range(world):
+        be.dx_reduce_peer(probs[g], 0, N, ws[g], tables[g], dtype, 1, 200)   # rank 0 runs out, rank 1 succeeds
+    for g in range(world):
+        be.dx_finish_peer(probs[g], 0, N, ws[g], tables[g], 1, dx[g], 200)
+    torch.cuda.synchronize()
+    for g in range(world):
+        assert be.read_status(ws[g]) == -6, f"rank {g} must report the timeout"
+        assert torch.all(dx[g] == 7.0), f"rank {g} must not have copied anything"
+
+
 def test_peer_exchange_refuses_what_it_cannot_do():
     be = ops.get_backend()
     prob = _native.Problem(n_rows_total=384, chunk_rows=384, hidden=256, vocab_local=1024, vocab_offset=0,

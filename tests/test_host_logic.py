@@ -237,6 +237,60 @@ def test_peer_exchange_sequencing_in_the_chunk_loop(fake):
     assert asked == []
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_collective_sequence_of_a_sharded_pass_does_not_depend_on_the_slab_mode(fake, monkeypatch, dtype):
+    """Each rank of a sharded run picks its slab mode by itself (own re-run counters, a polled event), so ranks can
+    be in different modes in the same pass. The sequence and sizes of the collectives (and the epochs of the peer
+    exchange) must then still be the same on all of them, or NCCL would pair up different calls."""
+    from linear_cross_entropy_loss_b200 import _native
+
+    x, y, W = make(N=2048, H=256, V=512)
+    x, W = x.to(dtype), W.to(dtype)
+
+    def sequence(mode):
+        monkeypatch.setattr(ops.slab_mode_policy, "choose",
+                            lambda key, dt: _native.SLAB_PER_TILE if dt == torch.float16 else mode)
+        seq = []
+
+        def gather(t):
+            seq.append(("all_gather", t.numel()))
+            return t
+
+        shard = ops.ShardSpec(rank=0, world=1, vocab_offset=0, gather_row_parts=gather,
+                              reduce_dx=lambda rows: seq.append(("all_reduce", tuple(rows.shape))))
+        ops.run_pass(x, y, W, -1, 0.0, 1.0, 1024, False, True, shard=shard)
+        return seq
+
+    by_row, by_tile = sequence(_native.SLAB_DEFAULT), sequence(_native.SLAB_PER_TILE)
+    assert by_row == by_tile and len(by_row) >= 4
+    # fp16 (always per tile, on every rank) keeps its half chunks; the other types run whole chunks when sharded
+    halves = dtype == torch.float16
+    assert by_row.count(("all_reduce", (512 if halves else 1024, 256))) == (4 if halves else 2)
+
+
+@pytest.mark.parametrize("V", [768, 808, 1003])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_multi_chunk_dW_is_narrowed_in_place_and_compacted(fake, dtype, V):
+    """More than one chunk: the last dw_chunk call gets the accumulator itself as its output (no second (H, V) buffer
+    while the workspace is alive) and the pass returns a plain, tightly packed dW in W's dtype -- for whole tiles, a
+    ragged last tile, and a vocabulary whose rows need padding to 8 columns."""
+    x, y, W = make(N=640, H=256, V=V, dtype=dtype)
+    seen = []
+    real = fake.dw_chunk
+
+    def spy(prob, x_, row0, rows, ws, acc, first, final):
+        seen.append((first, None if final is None else final.data_ptr() == acc.data_ptr()))
+        return real(prob, x_, row0, rows, ws, acc, first, final)
+
+    fake.dw_chunk = spy
+    out5, dx, dW, ws = ops.run_pass(x, y, W, -1, 0.0, 1.0, 256, False, True)
+    assert seen == [(True, None), (False, None), (False, True)] and ws is None
+    assert dW.dtype == dtype and dW.shape == (256, V) and dW.stride(1) == 1
+    want = oracle.forward_backward(x, y, W, -1).dW
+    tol = {torch.float32: 2e-7, torch.float16: 2e-3, torch.bfloat16: 1e-2}[dtype]
+    assert np.abs(dW.double().numpy() - want).max() <= tol * np.abs(want).max()
+
+
 def test_slab_mode_policy_decisions(monkeypatch):
     """The mode picker on its own: fp16 always per tile; bf16 per row until a finished pass reported that more
     than a quarter of its row groups were recomputed; a retry of the default mode every 64th pass; env overrides."""

@@ -11,6 +11,7 @@ import pytest
 import torch
 
 from linear_cross_entropy_loss_b200 import _native, ops
+from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -48,6 +49,11 @@ def test_static_scratch_entry_matches_the_workspace_path_twice_in_a_row():
     want = workspace_loss(x, y, W, -1, 1e-4, 0.5, True, 1024)
     torch.cuda.synchronize()
     assert torch.allclose(got, want, rtol=2e-5, atol=1e-6), (got, want)
+    # and against the float64 oracle directly, so that this file stands on its own
+    ref = oracle.forward_backward(x, y, W, -1, 1e-4, 0.5, want_grad=False)
+    assert abs(got[0].item() - ref.loss) <= 2e-5 * abs(ref.loss), (got[0].item(), ref.loss)
+    assert abs(got[1].item() - ref.z_value) <= 4e-5 * abs(ref.z_value)
+    assert abs(got[3].item() - ref.logit_entropy) <= 1e-3 * abs(ref.logit_entropy)
 
     # second call, different shape, dtype and options: must not see anything of the first call
     x2, y2, W2 = problem(1, 640, 256, 4096, torch.float16)
