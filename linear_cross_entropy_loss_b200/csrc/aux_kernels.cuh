@@ -420,7 +420,8 @@ template <>
 __device__ __forceinline__ float cast_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
 // Row-reference mode, after the log-sum-exp is known. One block per row:
-//   C_i = valid_i * exp(ref_i - lse_i) * (1 + 2 z_reg lse_i)        -> row_coef[i]   (factor of dx)
+//   C_i = valid_i * exp(ref_i - lse_i) * (1 + 2 z_reg lse_i)        -> row_coef[i]   (factor of dx), moved to the
+//         nearest value whose reciprocal is a T number
 //   xs[i, :] = C_i * x[i, :]                                        (A operand of dW = xs^T slab)
 //   slab[i, y_i] -= 1 / C_i   if this rank owns column y_i          (so that C_i * slab[i, :] = dZ[i, :])
 // ref_i is the base the row's partials were computed with (parts[0]).
@@ -439,12 +440,21 @@ row_finish_kernel(const T* __restrict__ x, long long x_ld, T* __restrict__ xs, l
   const float l = exists ? lse[r] : 0.f;
   float C = valid ? __expf(ref[r] - l) * (1.f + 2.f * z_regularization * l) : 0.f;
   if (valid && fabsf(C) < 1e-30f) C = (C < 0.f) ? -1e-30f : 1e-30f;  // keeps 1 / C finite
+  // The label entry carries the dominant term of the row's gradient (softmax - 1 is close to -1 there), so it is
+  // kept exact: the factor is nudged (by at most half an ulp of T, the size of the rounding every softmax entry
+  // gets anyway) to the nearest value whose reciprocal is representable in T. slab[i, y_i] - 1 / C then rounds
+  // with an error relative to the softmax entry, not to 1 / C, and C * (that entry) is -1 + softmax to fp32 accuracy.
+  float rcp = 0.f;
+  if (valid) {
+    rcp = cast_to_float<T>(cast_from_float<T>(1.f / C));
+    C = 1.f / rcp;
+  }
   if (threadIdx.x == 0) {
     row_coef[r] = C;
     const long long yl = yv - vocab_offset;
     if (valid && yl >= 0 && yl < vocab_local) {
       T* e = slab + (long long)r * slab_ld + yl;
-      *e = cast_from_float<T>(cast_to_float<T>(*e) - 1.f / C);
+      *e = cast_from_float<T>(cast_to_float<T>(*e) - rcp);
     }
   }
   const T* src = x + (long long)r * x_ld;

@@ -56,7 +56,13 @@ struct GemmShared {
   int abort_flag;
 };
 
-constexpr size_t kGemmSmemBytes = size_t(kStages) * kStageBytes + 1024 /*alignment slack*/ + sizeof(GemmShared);
+// Output staging for TMA stores: each of the four epilogue warps owns two buffers of 32 rows x 128 bytes
+// (128-byte swizzle), filled from registers and drained by cp.async.bulk.tensor stores / reduce-adds.
+constexpr int kStoreStageBytes = 32 * 128;
+constexpr int kStoreStagingBytes = 4 * 2 * kStoreStageBytes;  // 32 KiB per CTA
+
+constexpr size_t kGemmSmemBytes =
+    size_t(kStages) * kStageBytes + kStoreStagingBytes + 1024 /*alignment slack*/ + sizeof(GemmShared);
 
 struct GemmParams {
   // tile grid; units = splits * n_tiles * m_tiles, walked in the order n_fastest selects
@@ -113,6 +119,13 @@ struct GemmParams {
   // 256-row groups; group g covers rows [256 g, 256 g + 256) counted from row -run_mask_row0 of this call
   const int* run_mask;
   int run_mask_row0;
+
+  // ---- output through shared memory and TMA (the third tensor map of the launch): EPI_FWD slab stores;
+  // EPI_F32 tile stores (accumulate == 0) or reduce-adds at the memory side (accumulate == 1) of plain fp32 output
+  // (no out_final, no peer scatter). The map describes exactly what exists, so TMA clips tiles at the edges.
+  int out_tma;
+  int c_row0;                  // row of the map that row 0 of this launch's output corresponds to
+  int c_split_rows;            // EPI_F32: rows of the map between the outputs of consecutive K-splits
 
   int* status;                 // device status word (0 = ok)
   int tile_mode;               // forward epilogue: 1 = exp(z - tile max) even for bf16 / fp32
@@ -213,6 +226,90 @@ __device__ __forceinline__ void store_slab_chunk(float* dst, const float (&e)[32
   }
 }
 
+// One epilogue warp's pair of staging buffers. Lane l owns row l of the 32-row box: it writes its 128 bytes as eight
+// 16-byte pieces (piece j lands at j ^ (l & 7), the 128-byte swizzle TMA expects), then lane 0 issues the store.
+struct WarpStage {
+  uint8_t* base;  // 2 * kStoreStageBytes, 1024-byte aligned
+  int fills;      // boxes committed so far; selects the buffer
+
+  // The buffer to fill next, once the store that last read it has finished reading (at most one newer store, the
+  // one from the other buffer, may still be in flight).
+  __device__ __forceinline__ uint8_t* acquire(int lane) {
+    if (lane == 0) bulk_wait_group_read<1>();
+    __syncwarp();
+    return base + (fills & 1) * kStoreStageBytes;
+  }
+  static __device__ __forceinline__ void put(uint8_t* buf, int lane, int piece, uint32_t a, uint32_t b, uint32_t c,
+                                             uint32_t d) {
+    st_shared_128(buf + lane * 128 + ((piece ^ (lane & 7)) << 4), a, b, c, d);
+  }
+  // Box (c0 = first column, c1 = first row) of the tensor map; reduce: global += box instead of global = box.
+  __device__ __forceinline__ void commit(const CUtensorMap* tm, const uint8_t* buf, int lane, int c0, int c1,
+                                         bool reduce) {
+    fence_proxy_async_smem();  // the generic-proxy writes above become visible to the TMA unit
+    __syncwarp();
+    if (lane == 0) {
+      if (reduce)
+        tma_reduce_add_2d(tm, buf, c0, c1);
+      else
+        tma_store_2d(tm, buf, c0, c1);
+      bulk_commit_group();
+    }
+    ++fills;
+  }
+  // Before the kernel ends: every store of this warp has been performed.
+  __device__ __forceinline__ void drain(int lane) {
+    if (lane == 0) bulk_wait_group<0>();
+    __syncwarp();
+  }
+};
+
+// 32 consecutive slab elements of this lane's row into the staging buffer: 16-bit types fill one half of the
+// 128-byte row (pieces 4 * half .. 4 * half + 3), fp32 fills all of it.
+__device__ __forceinline__ void stage_slab_chunk(__half*, uint8_t* buf, int lane, int half, const float (&e)[32]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint32_t v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      __half2 h = __floats2half2_rn(e[8 * q + 2 * k], e[8 * q + 2 * k + 1]);
+      v[k] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    WarpStage::put(buf, lane, 4 * half + q, v[0], v[1], v[2], v[3]);
+  }
+}
+__device__ __forceinline__ void stage_slab_chunk(__nv_bfloat16*, uint8_t* buf, int lane, int half,
+                                                 const float (&e)[32]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint32_t v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(e[8 * q + 2 * k], e[8 * q + 2 * k + 1]);
+      v[k] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    WarpStage::put(buf, lane, 4 * half + q, v[0], v[1], v[2], v[3]);
+  }
+}
+__device__ __forceinline__ void stage_slab_chunk(float*, uint8_t* buf, int lane, int /*half*/, const float (&e)[32]) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q)
+    WarpStage::put(buf, lane, q, __float_as_uint(e[4 * q]), __float_as_uint(e[4 * q + 1]),
+                   __float_as_uint(e[4 * q + 2]), __float_as_uint(e[4 * q + 3]));
+}
+
+// Chunk c (32 columns) of a 256-column tile of the slab, through the staging buffers: two chunks of a 16-bit slab
+// (one chunk of an fp32 slab) make one 128-byte-wide box of 32 rows.
+template <typename Elem>
+__device__ __forceinline__ void slab_chunk_via_tma(const GemmParams& p, const CUtensorMap* tmC, WarpStage& stage,
+                                                   uint8_t*& buf, int lane, int c, int col0, int row0,
+                                                   const float (&e)[32]) {
+  constexpr bool kHalves = sizeof(Elem) == 2;
+  if (!kHalves || (c & 1) == 0) buf = stage.acquire(lane);
+  stage_slab_chunk(static_cast<Elem*>(nullptr), buf, lane, c & 1, e);
+  if (!kHalves || (c & 1) == 1) stage.commit(tmC, buf, lane, col0 + (kHalves ? (c - 1) : c) * 32, row0, false);
+}
+
 // Forward epilogue. For its row i and this tile's 256 columns j (z = scale * acc):
 //   tile_max = max_j z,  tile_sum = sum_j exp(z - tile_max),  slab[i, j] = exp(z - tile_max)
 //   target_logit[i] = z[i, y_i] if column y_i lies in this tile
@@ -220,8 +317,8 @@ __device__ __forceinline__ void store_slab_chunk(float* dst, const float (&e)[32
 // Two passes over the accumulator (max first). Used for fp16, whose narrow exponent range needs the
 // exponentials normalised per tile; the slab is rescaled to the row's log-sum-exp afterwards.
 template <int kKind, bool kMonitor>
-__device__ __forceinline__ void epilogue_forward_tilemax(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk,
-                                                         int row_in_tile) {
+__device__ __forceinline__ void epilogue_forward_tilemax(const GemmParams& p, const CUtensorMap* tmC, WarpStage& stage,
+                                                         uint32_t taddr, int m_blk, int n_blk, int row_in_tile) {
   using Elem = typename SlabElem<kKind>::type;
   const long long r = (long long)m_blk * BLOCK_M + row_in_tile;
   const bool row_ok = r < p.rows_valid;                       // padding rows have no label and store no statistics
@@ -257,6 +354,7 @@ __device__ __forceinline__ void epilogue_forward_tilemax(const GemmParams& p, ui
   const float neg_m = -mx * sl2;
   float s = 0.f, ez = 0.f;
   Elem* slab_row = reinterpret_cast<Elem*>(p.slab) + r * p.slab_ld + (long long)n_blk * BLOCK_N;
+  uint8_t* stage_buf = nullptr;
 #pragma unroll 1
   for (int c = 0; c < BLOCK_N / 32; ++c) {
     uint32_t v[32];
@@ -271,7 +369,13 @@ __device__ __forceinline__ void epilogue_forward_tilemax(const GemmParams& p, ui
       s += e[i];
       if (kMonitor && i < lim) ez = fmaf(e[i], f, ez);
     }
-    if (p.store_slab) store_slab_chunk(slab_row + c * 32, e);
+    if (p.store_slab) {
+      if (p.out_tma)
+        slab_chunk_via_tma<Elem>(p, tmC, stage, stage_buf, row_in_tile & 31, c, n_blk * BLOCK_N,
+                                 p.c_row0 + m_blk * BLOCK_M + (row_in_tile & ~31), e);
+      else
+        store_slab_chunk(slab_row + c * 32, e);
+    }
   }
 
   if (row_ok) {
@@ -294,8 +398,8 @@ __device__ __forceinline__ void epilogue_forward_tilemax(const GemmParams& p, ui
 // PER-ROW factor: the slab feeds the gradient GEMMs as it is. If |row max - ref_i| turns out to exceed 60 the
 // host-side sequence re-runs the chunk with ref_i = row max (see row_stats_rowref_kernel).
 template <int kKind, bool kMonitor>
-__device__ __forceinline__ void epilogue_forward_rowref(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk,
-                                                        int row_in_tile) {
+__device__ __forceinline__ void epilogue_forward_rowref(const GemmParams& p, const CUtensorMap* tmC, WarpStage& stage,
+                                                        uint32_t taddr, int m_blk, int n_blk, int row_in_tile) {
   using Elem = typename SlabElem<kKind>::type;
   const long long r = (long long)m_blk * BLOCK_M + row_in_tile;
   const bool row_ok = r < p.rows_valid;                       // padding rows have no label and store no statistics
@@ -309,6 +413,7 @@ __device__ __forceinline__ void epilogue_forward_rowref(const GemmParams& p, uin
 
   float mx = -INFINITY, s = 0.f, ez = 0.f, sq = 0.f, tv = 0.f;
   Elem* slab_row = reinterpret_cast<Elem*>(p.slab) + r * p.slab_ld + (long long)n_blk * BLOCK_N;
+  uint8_t* stage_buf = nullptr;
 #pragma unroll 1
   for (int c = 0; c < BLOCK_N / 32; ++c) {
     uint32_t v[32];
@@ -350,7 +455,13 @@ __device__ __forceinline__ void epilogue_forward_rowref(const GemmParams& p, uin
       for (int i = 0; i < 32; ++i)
         if (i == sel) tv = __uint_as_float(v[i]);
     }
-    if (p.store_slab) store_slab_chunk(slab_row + c * 32, e);
+    if (p.store_slab) {
+      if (p.out_tma)
+        slab_chunk_via_tma<Elem>(p, tmC, stage, stage_buf, row_in_tile & 31, c, n_blk * BLOCK_N,
+                                 p.c_row0 + m_blk * BLOCK_M + (row_in_tile & ~31), e);
+      else
+        store_slab_chunk(slab_row + c * 32, e);
+    }
   }
 
   if (row_ok) {
@@ -372,19 +483,19 @@ struct ForwardMode {
 };
 
 template <int kKind, bool kMonitor>
-__device__ __forceinline__ void epilogue_forward(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk,
-                                                 int row_in_tile) {
+__device__ __forceinline__ void epilogue_forward(const GemmParams& p, const CUtensorMap* tmC, WarpStage& stage,
+                                                 uint32_t taddr, int m_blk, int n_blk, int row_in_tile) {
   if (ForwardMode<kKind>::kRowRef && !p.tile_mode)
-    epilogue_forward_rowref<kKind, kMonitor>(p, taddr, m_blk, n_blk, row_in_tile);
+    epilogue_forward_rowref<kKind, kMonitor>(p, tmC, stage, taddr, m_blk, n_blk, row_in_tile);
   else
-    epilogue_forward_tilemax<kKind, kMonitor>(p, taddr, m_blk, n_blk, row_in_tile);
+    epilogue_forward_tilemax<kKind, kMonitor>(p, tmC, stage, taddr, m_blk, n_blk, row_in_tile);
 }
 
 // Plain fp32 epilogue: result = coef * acc (+ out[split][row, col] when accumulating); the result is stored
 // to out, or -- converted to the input element type -- to out_final when that is given.
 template <int kKind>
-__device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr, int m_blk, int n_blk, int split,
-                                             int row_in_tile) {
+__device__ __forceinline__ void epilogue_f32(const GemmParams& p, const CUtensorMap* tmC, WarpStage& stage,
+                                             uint32_t taddr, int m_blk, int n_blk, int split, int row_in_tile) {
   using Elem = typename SlabElem<kKind>::type;
   const long long row = (long long)m_blk * BLOCK_M + row_in_tile;
   const bool row_ok = row < p.out_rows;
@@ -412,7 +523,17 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, uint32_t taddr
     tmem_ld_wait();
     const int lim = ncols - c * 32;
     float r[32];
-    if (p.peer_rows_own > 0) {
+    if (p.out_tma) {
+      // plain fp32 output: this warp's 32 rows x 32 columns go through shared memory and one TMA store (or one
+      // reduce-add, performed at the memory side, when accumulating); TMA drops what lies outside the output
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] = coef * __uint_as_float(v[i]);
+      const int lane = row_in_tile & 31;
+      uint8_t* buf = stage.acquire(lane);
+      stage_slab_chunk(static_cast<float*>(nullptr), buf, lane, 0, r);
+      stage.commit(tmC, buf, lane, n_blk * BLOCK_N + c * 32,
+                   p.c_row0 + split * p.c_split_rows + m_blk * BLOCK_M + (row_in_tile & ~31), p.accumulate != 0);
+    } else if (p.peer_rows_own > 0) {
       // Scatter to the owning rank (whole padded tiles, so no masks). A thread holds 128 contiguous bytes of
       // ITS row, and storing them as they are gives 32 separate 32-byte segments per warp instruction, which a
       // link to another GPU carries poorly. So the four lanes of a group first exchange 32-byte units --
@@ -502,7 +623,7 @@ __device__ __forceinline__ bool tile_selected(const GemmParams& p, int row0, int
 template <int kKind, bool kAMN, bool kBMN, int kEpi, bool kMonitor>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   constexpr int ES = (kKind == KIND_TF32) ? 4 : 2;  // operand element size in bytes
   constexpr int BLOCK_K = 128 / ES;                 // elements of K per 128-byte swizzle row
   constexpr int UMMA_K = 32 / ES;                   // K elements per tcgen05.mma
@@ -515,7 +636,8 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  GemmShared* sh = reinterpret_cast<GemmShared*>(tiles + size_t(kStages) * kStageBytes);
+  uint8_t* staging = tiles + size_t(kStages) * kStageBytes;  // 1024-byte aligned: the ring is a multiple of 1024 bytes
+  GemmShared* sh = reinterpret_cast<GemmShared*>(staging + kStoreStagingBytes);
   volatile int* abort_flag = &sh->abort_flag;
   if (p.run_if != nullptr && *p.run_if == 0) return;  // uniform over the grid: nothing has been set up yet
 
@@ -537,6 +659,7 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(&sh->tmem_base, kTmemCols);
@@ -656,6 +779,7 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // ------------------------------------------------------------------ epilogue warps
     const int lane_group = warp & 3;  // a warp may only touch TMEM lanes [32 * (warp % 4), +32)
     const int row_in_tile = lane_group * 32 + lane;
+    WarpStage stage{staging + lane_group * 2 * kStoreStageBytes, 0};
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
@@ -671,9 +795,9 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + uint32_t(acc * BLOCK_N);
       if (kEpi == EPI_FWD)
-        epilogue_forward<kKind, kMonitor>(p, taddr, m_blk, n_blk, row_in_tile);
+        epilogue_forward<kKind, kMonitor>(p, &tmC, stage, taddr, m_blk, n_blk, row_in_tile);
       else
-        epilogue_f32<kKind>(p, taddr, m_blk, n_blk, split, row_in_tile);
+        epilogue_f32<kKind>(p, &tmC, stage, taddr, m_blk, n_blk, split, row_in_tile);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
@@ -682,6 +806,7 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         acc_phase ^= 1u;
       }
     }
+    stage.drain(lane);  // this warp's TMA stores have been performed before the CTA's shared memory goes away
   }
 
   // ------------------------------------------------------------------ teardown
@@ -730,7 +855,9 @@ struct GemmPairShared {
   int abort_flag;
 };
 
-constexpr size_t kGemmPairSmemBytes = size_t(kPairStages) * kPairStageBytes + 1024 + sizeof(GemmPairShared);
+constexpr size_t kGemmPairSmemBytes =
+    size_t(kPairStages) * kPairStageBytes + kStoreStagingBytes + 1024 + sizeof(GemmPairShared);
+static_assert(kGemmPairSmemBytes <= 232448, "dynamic shared memory limit of sm_100");
 
 template <int kKind, bool kAMN, bool kBMN>
 __host__ __device__ constexpr uint32_t make_instr_desc_pair() {
@@ -743,7 +870,7 @@ __host__ __device__ constexpr uint32_t make_instr_desc_pair() {
 template <int kKind, bool kAMN, bool kBMN, int kEpi, bool kMonitor>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const GemmParams p) {
+                     const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   constexpr int ES = (kKind == KIND_TF32) ? 4 : 2;
   constexpr int BLOCK_K = 128 / ES;
   constexpr int UMMA_K = 32 / ES;
@@ -756,7 +883,8 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  GemmPairShared* sh = reinterpret_cast<GemmPairShared*>(tiles + size_t(kPairStages) * kPairStageBytes);
+  uint8_t* staging = tiles + size_t(kPairStages) * kPairStageBytes;  // 1024-byte aligned: the ring is a multiple of 1024 bytes
+  GemmPairShared* sh = reinterpret_cast<GemmPairShared*>(staging + kStoreStagingBytes);
   volatile int* abort_flag = &sh->abort_flag;
   if (p.run_if != nullptr && *p.run_if == 0) return;  // uniform over the grid: nothing has been set up yet
 
@@ -782,6 +910,7 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc_pair(&sh->tmem_base, kTmemCols);
@@ -905,6 +1034,7 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     // ------------------------------------------------------------------ epilogue warps (both CTAs)
     const int lane_group = warp & 3;
     const int row_in_tile = lane_group * 32 + lane;
+    WarpStage stage{staging + lane_group * 2 * kStoreStageBytes, 0};
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int unit = cluster_id; unit < units; unit += n_clusters) {
@@ -921,9 +1051,9 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + uint32_t(acc * BLOCK_N);
       if (kEpi == EPI_FWD)
-        epilogue_forward<kKind, kMonitor>(p, taddr, m_blk128, n_blk, row_in_tile);
+        epilogue_forward<kKind, kMonitor>(p, &tmC, stage, taddr, m_blk128, n_blk, row_in_tile);
       else
-        epilogue_f32<kKind>(p, taddr, m_blk128, n_blk, split, row_in_tile);
+        epilogue_f32<kKind>(p, &tmC, stage, taddr, m_blk128, n_blk, split, row_in_tile);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&sh->acc_empty[acc]), 0));
@@ -932,6 +1062,7 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         acc_phase ^= 1u;
       }
     }
+    stage.drain(lane);
   }
 
   // ------------------------------------------------------------------ teardown

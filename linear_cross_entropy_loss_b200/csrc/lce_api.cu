@@ -10,6 +10,7 @@
 #include <atomic>
 #include <cstddef>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -239,6 +240,21 @@ int make_operand_tmap(CUtensorMap* map, int dtype, bool mn_major, const void* ba
                   : make_tmap(map, dtype, base, inner, outer, ld, per128, tile_mn, false);
 }
 
+// Output tile map for the epilogues' TMA stores: boxes of 32 rows x 128 bytes of a row-major [outer, inner] tensor.
+int make_store_tmap(CUtensorMap* map, int dtype, const void* base, long long inner, long long outer, long long ld) {
+  return make_tmap(map, dtype, base, inner, outer, ld, 128 / elem_size(dtype), 32, false);
+}
+
+// LCE_EPILOGUE_STORE=direct (read once, at the first launch) keeps the epilogues on per-thread global stores
+// instead of shared-memory staging + TMA; for A/B measurements of the two forms.
+bool epilogue_tma_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("LCE_EPILOGUE_STORE");
+    return !(v != nullptr && std::strcmp(v, "direct") == 0);
+  }();
+  return on;
+}
+
 // ------------------------------------------------------------------------------------------------
 // launches
 // ------------------------------------------------------------------------------------------------
@@ -291,8 +307,8 @@ int rows_of_b_tile(bool pair) { return pair ? BLOCK_N / 2 : BLOCK_N; }
 
 // gp.m_tiles counts 128-row tiles; `pair` must be the value the tensor maps were built for.
 template <int kKind, bool kAMN, bool kBMN, int kEpi, bool kMon>
-int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& gp_in, int sms, cudaStream_t st,
-                bool pair) {
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& gp_in, int sms,
+                cudaStream_t st, bool pair) {
   GemmParams gp = gp_in;
   if (pair && gp.m_tiles % 2 != 0) return LCE_ERR_INVALID_ARGUMENT;
   if (pair) gp.m_tiles /= 2;
@@ -301,21 +317,21 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
   if (pair) {
     const long long clusters = units < sms / 2 ? units : sms / 2;
     lce_gemm_pair_kernel<kKind, kAMN, kBMN, kEpi, kMon>
-        <<<(int)(2 * clusters), kGemmThreads, kGemmPairSmemBytes, st>>>(ta, tb, gp);
+        <<<(int)(2 * clusters), kGemmThreads, kGemmPairSmemBytes, st>>>(ta, tb, tc, gp);
   } else {
     const int grid = (int)(units < sms ? units : sms);
-    lce_gemm_kernel<kKind, kAMN, kBMN, kEpi, kMon><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(ta, tb, gp);
+    lce_gemm_kernel<kKind, kAMN, kBMN, kEpi, kMon><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(ta, tb, tc, gp);
   }
   return check_launch();
 }
 
 template <bool kAMN, bool kBMN, int kEpi, bool kMon>
-int launch_gemm_dtype(int dtype, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& gp, int sms,
-                      cudaStream_t st, bool pair) {
+int launch_gemm_dtype(int dtype, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                      const GemmParams& gp, int sms, cudaStream_t st, bool pair) {
   switch (dtype) {
-    case LCE_DTYPE_F16: return launch_gemm<KIND_F16, kAMN, kBMN, kEpi, kMon>(ta, tb, gp, sms, st, pair);
-    case LCE_DTYPE_BF16: return launch_gemm<KIND_BF16, kAMN, kBMN, kEpi, kMon>(ta, tb, gp, sms, st, pair);
-    case LCE_DTYPE_F32: return launch_gemm<KIND_TF32, kAMN, kBMN, kEpi, kMon>(ta, tb, gp, sms, st, pair);
+    case LCE_DTYPE_F16: return launch_gemm<KIND_F16, kAMN, kBMN, kEpi, kMon>(ta, tb, tc, gp, sms, st, pair);
+    case LCE_DTYPE_BF16: return launch_gemm<KIND_BF16, kAMN, kBMN, kEpi, kMon>(ta, tb, tc, gp, sms, st, pair);
+    case LCE_DTYPE_F32: return launch_gemm<KIND_TF32, kAMN, kBMN, kEpi, kMon>(ta, tb, tc, gp, sms, st, pair);
   }
   return LCE_ERR_INVALID_ARGUMENT;
 }
@@ -413,6 +429,14 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
 
   GemmParams gp;
   memset(&gp, 0, sizeof(gp));
+  // the slab leaves the epilogue through shared memory and TMA stores: whole 128-byte lines instead of one 32-byte
+  // sector per thread and instruction
+  CUtensorMap tc = ta;
+  if (p->want_grad && w.slab != nullptr && epilogue_tma_enabled()) {
+    if ((v = make_store_tmap(&tc, p->dtype, w.slab, v_pad, p->chunk_rows, v_pad)) != LCE_OK) return v;
+    gp.out_tma = 1;
+    gp.c_row0 = (int)local0;
+  }
   gp.m_tiles = (int)(rows_pad / BLOCK_M);
   gp.n_tiles = (int)(v_pad / BLOCK_N);
   gp.splits = 1;
@@ -440,8 +464,8 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
   const long long* lab = reinterpret_cast<const long long*>(labels) + row0;
   float* parts = row_parts_local + local0;
   auto launch_forward = [&]() {
-    return p->monitoring ? launch_gemm_dtype<false, true, EPI_FWD, true>(p->dtype, ta, tb, gp, sms, st, pair)
-                         : launch_gemm_dtype<false, true, EPI_FWD, false>(p->dtype, ta, tb, gp, sms, st, pair);
+    return p->monitoring ? launch_gemm_dtype<false, true, EPI_FWD, true>(p->dtype, ta, tb, tc, gp, sms, st, pair)
+                         : launch_gemm_dtype<false, true, EPI_FWD, false>(p->dtype, ta, tb, tc, gp, sms, st, pair);
   };
   auto run_forward = [&]() {  // timed when profiling is on; the conditional re-run below is not
     ProfScope prof(PROF_FWD, st);
@@ -472,7 +496,7 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
     GemmParams pp = gp;
     pp.n_tiles = kProbeTiles;
     pp.store_slab = 0;
-    if ((v = launch_gemm_dtype<false, true, EPI_FWD, false>(p->dtype, ta, tb, pp, sms, st, pair)) != LCE_OK) return v;
+    if ((v = launch_gemm_dtype<false, true, EPI_FWD, false>(p->dtype, ta, tb, tc, pp, sms, st, pair)) != LCE_OK) return v;
     probe_ref_kernel<<<(int)((rows + 255) / 256), 256, 0, st>>>(gp.tile_max, p->chunk_rows, kProbeTiles, (int)rows,
                                                                w.row_ref + local0);
     if ((v = check_launch()) != LCE_OK) return v;
@@ -651,6 +675,16 @@ int launch_dx_gemm(const lce_problem* p, const void* weight, int64_t w_ld, int64
   gp.out_div = &w.scalars->n_valid;
   gp.row_coef = row_reference_mode(p) ? w.row_coef + local0 : nullptr;
   gp.status = &w.scalars->status;
+  CUtensorMap tc = ta;
+  if (scatter == nullptr && epilogue_tma_enabled()) {
+    // the partials [splits][chunk_rows][h_pad] seen as one fp32 matrix of splits * chunk_rows rows
+    if ((v = make_store_tmap(&tc, LCE_DTYPE_F32, w.dx_part, h_pad, (long long)w.dx_splits * p->chunk_rows, h_pad)) !=
+        LCE_OK)
+      return v;
+    gp.out_tma = 1;
+    gp.c_row0 = (int)local0;
+    gp.c_split_rows = (int)p->chunk_rows;
+  }
   if (scatter != nullptr) {
     for (int g = 0; g < scatter->world; ++g)
       gp.peer_out[g] = reinterpret_cast<float*>(scatter->bases.base[g] + scatter->layout.recv_off(scatter->buf));
@@ -659,7 +693,7 @@ int launch_dx_gemm(const lce_problem* p, const void* weight, int64_t w_ld, int64
     gp.peer_slot0 = scatter->rank * w.dx_splits;
   }
   ProfScope prof(PROF_DX, st);
-  return launch_gemm_dtype<false, false, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st, pair);
+  return launch_gemm_dtype<false, false, EPI_F32, false>(p->dtype, ta, tb, tc, gp, sms, st, pair);
 }
 
 long long peer_wait_limit_ns(int32_t wait_ms) { return (long long)(wait_ms > 0 ? wait_ms : 10000) * 1000000LL; }
@@ -902,9 +936,19 @@ int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0
   gp.out_final_ld = dwf_ld;
   gp.out_final_inplace = (inplace && p->dtype != LCE_DTYPE_F32) ? 1 : 0;  // fp32: the accumulator IS the result
   gp.status = &w.scalars->status;
+  // Chunks that only add into the fp32 accumulator do it through TMA: a tile store for the first chunk, reduce-adds
+  // performed at the memory side for the following ones (the SM never reads the accumulator). Each element gets
+  // exactly one add per chunk and the chunks are ordered by the stream, so the sum stays deterministic. The chunk
+  // that also converts to W's type reads the accumulator in its epilogue instead.
+  CUtensorMap tc = ta;
+  if (dweight_final == nullptr && epilogue_tma_enabled() &&
+      (reinterpret_cast<uintptr_t>(dweight_acc) & 15u) == 0 && ((dw_ld * 4) & 15) == 0) {
+    if ((v = make_store_tmap(&tc, LCE_DTYPE_F32, dweight_acc, p->vocab_local, p->hidden, dw_ld)) != LCE_OK) return v;
+    gp.out_tma = 1;
+  }
   {
     ProfScope prof(PROF_DW, st);
-    v = launch_gemm_dtype<true, true, EPI_F32, false>(p->dtype, ta, tb, gp, sms, st, pair);
+    v = launch_gemm_dtype<true, true, EPI_F32, false>(p->dtype, ta, tb, tc, gp, sms, st, pair);
   }
   return v;
 }
@@ -1067,12 +1111,20 @@ int lce_debug_gemm(int32_t dtype, int32_t a_mn_major, int32_t b_mn_major, const 
   gp.out_scale = 1.f;
   gp.status = dev_status;
   gp.clock_probe = reinterpret_cast<long long*>(dev_status + 2);
+  CUtensorMap tc = ta;
+  if (epilogue_tma_enabled() && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
+    if ((v = make_store_tmap(&tc, LCE_DTYPE_F32, out, n, (long long)splits * m, n)) != LCE_OK) return v;
+    gp.out_tma = 1;
+    gp.c_split_rows = (int)m;
+  }
   cudaStream_t st = (cudaStream_t)stream;
   if (!a_mn_major && !b_mn_major)
-    return launch_gemm_dtype<false, false, EPI_F32, false>(dtype, ta, tb, gp, sms, st, pair);
-  if (!a_mn_major && b_mn_major) return launch_gemm_dtype<false, true, EPI_F32, false>(dtype, ta, tb, gp, sms, st, pair);
-  if (a_mn_major && !b_mn_major) return launch_gemm_dtype<true, false, EPI_F32, false>(dtype, ta, tb, gp, sms, st, pair);
-  return launch_gemm_dtype<true, true, EPI_F32, false>(dtype, ta, tb, gp, sms, st, pair);
+    return launch_gemm_dtype<false, false, EPI_F32, false>(dtype, ta, tb, tc, gp, sms, st, pair);
+  if (!a_mn_major && b_mn_major)
+    return launch_gemm_dtype<false, true, EPI_F32, false>(dtype, ta, tb, tc, gp, sms, st, pair);
+  if (a_mn_major && !b_mn_major)
+    return launch_gemm_dtype<true, false, EPI_F32, false>(dtype, ta, tb, tc, gp, sms, st, pair);
+  return launch_gemm_dtype<true, true, EPI_F32, false>(dtype, ta, tb, tc, gp, sms, st, pair);
 }
 
 }  // extern "C"

@@ -49,7 +49,7 @@ def load():
     return _module
 
 
-def trim_configs(fwd_keep=(1, 5, 9), bwd_keep=(0, 2, 3)) -> None:
+def trim_configs(fwd_keep=(0, 9, 12), bwd_keep=(0, 2, 3)) -> None:
     """Shortens the autotune lists IN PLACE, the way the reference's README tells users to (README.md:37-38):
     the autotuners hold the very list objects the package exports. The kept backward entries have SPLIT_N = SPLIT_V
     = 1, the only ones the reference accepts for bf16 (ops.py:35-41)."""
