@@ -53,6 +53,10 @@ def parse_args():
     ap.add_argument("--n-chunk-size", type=int, default=0,
                     help="override the configuration's N_chunk_size (0 = keep it; the metric's point uses 4096)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1, rank 0)")
+    ap.add_argument("--no-parity", action="store_true",
+                    help="skip the float64 check of the last timed step's loss and gradients (after the timed region)")
+    ap.add_argument("--no-strong", action="store_true",
+                    help="skip the short strong-scaling sub-record on the 65536 x 4096 x 131072 LM-head configuration")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU work of the baseline leg")
     ap.add_argument("--triton-ref", choices=["full", "trimmed", "off"], default="full",
                     help="N=1: also time the reference's own Triton op on this GPU (outside the timed region of the "
@@ -222,6 +226,97 @@ def triton_reference_leg(cfg, x, y, W, mode):
         return {"unavailable": f"reference Triton unavailable on this box: {type(err).__name__}: {err}"[:600]}
 
 
+def parity_record(cfg, x, y, W, dx, dW, loss_value, rank, world, v_local):
+    """Correctness of the very tensors the timed steps produced, checked here in float64 (rows / columns subsets) and
+    float32-product / float64-reduction (the loss over all rows), with plain torch on the GPU. At world > 1 every
+    rank handles its own vocabulary slab and the pieces are combined with NCCL collectives, so this also covers the
+    sharded data path (row partials exchange, dx reduction) in the run that is being timed.
+    Returns {"loss_rel_err", "dx_cos", "dw_cos", "ok"}; tolerances: loss 1e-3 relative, cosines 0.9999."""
+    import torch
+    import torch.distributed as dist
+
+    dev = x.device
+    N, H = x.shape
+    scale, zreg, ign = cfg.logit_scale, cfg.z_regularization, cfg.ignore_index
+    off = rank * v_local
+    valid = y != ign
+    n_valid = int(valid.sum())
+    y_loc = y - off
+    owned = valid & (y_loc >= 0) & (y_loc < v_local)
+
+    def all_sum(t):
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return t
+
+    def all_max(t):
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t
+
+    # log-sum-exp and target logit of every row: float32 products (no TF32), float64 reductions
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    Wf = W.detach().float()
+    m_loc = torch.empty(N, dtype=torch.float64, device=dev)
+    s_loc = torch.empty(N, dtype=torch.float64, device=dev)
+    t_loc = torch.zeros(N, dtype=torch.float64, device=dev)
+    for r0 in range(0, N, 1024):
+        z = (x[r0:r0 + 1024].detach().float() @ Wf).double() * scale
+        m = z.max(dim=1).values
+        m_loc[r0:r0 + 1024] = m
+        s_loc[r0:r0 + 1024] = torch.exp(z - m[:, None]).sum(dim=1)
+        o = owned[r0:r0 + 1024]
+        t_loc[r0:r0 + 1024][o] = z[o, y_loc[r0:r0 + 1024][o]]
+        del z
+    del Wf
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    m_all = all_max(m_loc.clone())
+    lse = m_all + torch.log(all_sum(s_loc * torch.exp(m_loc - m_all)))
+    t_all = all_sum(t_loc)
+    want_loss = (((lse - t_all) * valid).sum() + zreg * ((lse * lse) * valid).sum()).item() / n_valid
+    loss_rel = abs(loss_value - want_loss) / abs(want_loss)
+
+    # dx of 32 rows (same rows on every rank) in float64
+    g = torch.Generator().manual_seed(1234)
+    rows = torch.randperm(N, generator=g)[:32].to(dev)
+    xs = x[rows].detach().double()
+    dx_rows = torch.zeros((32, H), dtype=torch.float64, device=dev)
+    for v0 in range(0, v_local, 16384):
+        Wb = W[:, v0:v0 + 16384].detach().double()
+        z = (xs @ Wb) * scale
+        dz = torch.exp(z - lse[rows][:, None]) * (1 + 2 * zreg * lse[rows])[:, None]
+        yl = y_loc[rows] - v0
+        hit = owned[rows] & (yl >= 0) & (yl < Wb.shape[1])
+        dz[hit.nonzero()[:, 0], yl[hit]] -= 1
+        dz *= valid[rows].double()[:, None]
+        dx_rows += dz @ Wb.T
+    dx_rows = all_sum(dx_rows) * (scale / n_valid)
+    got = dx[rows].double()
+    dx_cos = float((got * dx_rows).sum() / (got.norm() * dx_rows.norm() + 1e-300))
+
+    # 64 columns of this rank's dW in float64 (its four most frequent label columns among them, when it owns some)
+    cols = torch.cat([torch.arange(4), torch.randperm(v_local - 4, generator=g)[:60] + 4]).to(dev)
+    Wc = W[:, cols].detach().double()
+    want_dw = torch.zeros((H, 64), dtype=torch.float64, device=dev)
+    for r0 in range(0, N, 8192):
+        xb = x[r0:r0 + 8192].detach().double()
+        l = lse[r0:r0 + 8192]
+        dz = torch.exp((xb @ Wc) * scale - l[:, None]) * (1 + 2 * zreg * l)[:, None]
+        dz -= (y_loc[r0:r0 + 8192][:, None] == cols[None, :]).double()
+        dz *= valid[r0:r0 + 8192].double()[:, None]
+        want_dw += xb.T @ dz
+    want_dw *= scale / n_valid
+    got = dW[:, cols].double()
+    cos_t = torch.stack([(got * want_dw).sum(), (got * got).sum(), (want_dw * want_dw).sum()])
+    cos_t = all_sum(cos_t)  # one cosine over the columns of all ranks
+    dw_cos = float(cos_t[0] / (cos_t[1].sqrt() * cos_t[2].sqrt() + 1e-300))
+    ok = loss_rel <= 1e-3 and dx_cos >= 0.9999 and dw_cos >= 0.9999
+    return {"loss_rel_err": loss_rel, "dx_cos": dx_cos, "dw_cos": dw_cos, "ok": bool(ok),
+            "checked": "loss over all rows (fp32 products, fp64 reductions); dx of 32 rows and 64 dW columns per rank "
+                       "in float64; tolerances 1e-3 / 0.9999 / 0.9999"}
+
+
 def run_reference_arm(args, cfg, n_gpus):
     per_step = max(0.25, args.ref_budget / max(1, args.steps + args.warmup))
     tflops, ms, info = cpu_reference_rate(cfg, per_step, steps=args.steps, warmup=args.warmup)
@@ -299,7 +394,7 @@ def main():
     x.requires_grad_(True)
     W.requires_grad_(True)
 
-    def fwd_bwd(xx, yy):
+    def fwd_bwd(xx, yy, keep_grads=False):
         if sharded:
             loss = linear_cross_entropy_sharded(xx, yy, W, None, cfg.ignore_index, cfg.z_regularization,
                                                 cfg.logit_scale, cfg.N_chunk_size, cfg.monitoring)[0]
@@ -307,8 +402,9 @@ def main():
             loss = linear_cross_entropy(xx, yy, W, cfg.ignore_index, cfg.z_regularization, cfg.logit_scale,
                                         cfg.N_chunk_size, cfg.monitoring)[0]
         loss.backward()
-        xx.grad = None
-        W.grad = None
+        if not keep_grads:
+            xx.grad = None
+            W.grad = None
         return loss
 
     def barrier():
@@ -339,8 +435,8 @@ def main():
     barrier()
     sampler.mark_start()
     e0.record()
-    for _ in range(args.steps):
-        loss = fwd_bwd(x, y)
+    for i in range(args.steps):
+        loss = fwd_bwd(x, y, keep_grads=(i == args.steps - 1))  # the last timed step's gradients are checked below
     e1.record()
     barrier()
     sampler.mark_end()
@@ -353,6 +449,11 @@ def main():
     peak_extra = torch.cuda.max_memory_allocated() - mem_before
     value = cfg.flops / (ms_per_step * 1e-3) / 1e12
     loss_value = loss.item()
+    parity = None
+    if not args.no_parity:
+        parity = parity_record(cfg, x, y, W, x.grad, W.grad, loss_value, rank, world, v_local)
+    x.grad = None
+    W.grad = None
 
     # ---- end to end through the public call, inputs in pinned host memory ------------------------------
     # Input pipeline as a training loop would have it: two device buffers; the copy of step i+1's inputs is issued
@@ -435,7 +536,7 @@ def main():
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": x_host.numel() * x_host.element_size() + y_host.numel() * 8,
                 "d2h_bytes_per_step": 4},
-        "gpu_launches": launches, "roofline": roofline, "loss": loss_value,
+        "gpu_launches": launches, "roofline": roofline, "loss": loss_value, "parity": parity,
         "peak_extra_bytes": peak_extra, "peak_budget_bytes": min(cfg.N, cfg.N_chunk_size) * v_local * 4,
         # the same without the gradients the caller receives and the fp32 dW accumulator (which the reference keeps too)
         "peak_extra_bytes_excl_grads": peak_extra - cfg.N * cfg.H * x.element_size()
@@ -444,6 +545,44 @@ def main():
 
     if rank == 0 and world == 1 and args.triton_ref != "off":
         line["triton_reference"] = triton_reference_leg(cfg, x, y, W, args.triton_ref)
+    if not args.no_strong and args.config == "headline_bf16":
+        # The configuration the 8-GPU scaling target is quoted on (65536 x 4096 x 131072, bf16, Zipf labels), with
+        # its vocabulary split over the ranks: total work fixed, so value(N) / (N * value(1)) is the strong-scaling
+        # efficiency. A short run (2 warm-up + 3 timed steps) beside the main measurement.
+        del x, y, W, bufs, x_host, y_host
+        torch.cuda.empty_cache()
+        c4 = synthetic.CONFIGS["c4_llama8b_bf16"]
+        vl4 = c4.V // world
+        x4, y4, W4 = synthetic.make_inputs(c4, device=dev, vocab_slice=(rank * vl4, (rank + 1) * vl4) if sharded else None)
+        x4.requires_grad_(True)
+        W4.requires_grad_(True)
+
+        def step4():
+            if sharded:
+                l4 = linear_cross_entropy_sharded(x4, y4, W4, None, c4.ignore_index, c4.z_regularization,
+                                                  c4.logit_scale, c4.N_chunk_size, c4.monitoring)[0]
+            else:
+                l4 = linear_cross_entropy(x4, y4, W4, c4.ignore_index, c4.z_regularization, c4.logit_scale,
+                                          c4.N_chunk_size, c4.monitoring)[0]
+            l4.backward()
+            x4.grad = None
+            W4.grad = None
+            return l4
+
+        for _ in range(2):
+            step4()
+        barrier()
+        e0.record()
+        for _ in range(3):
+            l4 = step4()
+        e1.record()
+        barrier()
+        ms4 = max_over_ranks(e0.elapsed_time(e1)) / 3
+        line["strong_scaling_c4"] = {"config": "c4_llama8b_bf16: N=65536 H=4096 V=131072 bf16 N_chunk_size=8192, "
+                                               f"vocabulary split over {world} rank(s)",
+                                     "value": c4.flops / (ms4 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms4,
+                                     "steps": 3, "warmup": 2, "scaling": "strong", "loss": l4.item()}
+        del x4, y4, W4
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         _, _, info = cpu_reference_rate(cfg, args.cpu_seconds)
         line["cpu_baseline"] = info
@@ -452,6 +591,8 @@ def main():
     if sharded:
         dist.barrier()
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        sys.exit(3)  # the timed steps produced results outside the stated tolerance
 
 
 if __name__ == "__main__":

@@ -64,7 +64,9 @@ typedef struct lce_problem {
   float logit_scale;      /* z = logit_scale * (x @ W)  (ops.py:200)               */
   float z_regularization; /* weight of mean(lse^2)       (ops.py:756-761)          */
   int32_t slab_mode;      /* LCE_SLAB_* : how the exponentials kept between forward and backward are normalised */
-  int32_t reserved;       /* must be 0                                             */
+  int32_t chunk_buffers;  /* 0 or 1: one set of per-chunk buffers (slab, statistics) in the workspace; 2: two sets,
+                             used alternately by consecutive chunks, so that lce_forward_chunk of chunk c + 1 may
+                             be enqueued before the combine / backward calls of chunk c (see lce_combine_chunk_peer) */
 } lce_problem;
 
 /* slab_mode. The forward keeps exp(z - b) of the chunk in the element type of the inputs (the "slab").
@@ -196,6 +198,34 @@ int lce_dx_reduce_peer(const lce_problem* p, int64_t row0, int64_t rows, void* w
                        int32_t dx_dtype, uint32_t epoch, int32_t wait_ms, void* stream);
 int lce_dx_finish_peer(const lce_problem* p, int64_t row0, int64_t rows, void* workspace, const lce_peer_table* peers,
                        uint32_t epoch, void* dx, int64_t dx_ld, int32_t dx_dtype, int32_t wait_ms, void* stream);
+
+/* ---- row statistics exchange between the ranks of a vocabulary-sharded run, over peer-mapped memory -------
+ * No counterpart in the reference (it has no multi-GPU path). These calls replace the all-gather of the per-row
+ * partials that a sharded caller would otherwise issue between lce_forward_chunk and lce_combine_chunk: each rank
+ * STORES its LCE_ROW_PARTS x rows partials into every rank's exchange buffer and publishes a 32-bit flag; the
+ * combine step waits (bounded) for the flags of all ranks and merges the partials in rank order, so every rank
+ * computes bitwise the same log-sum-exp. Only stores and flags cross the links.
+ *
+ * Used with chunk_buffers == 2 this takes the exchange off the critical path: the caller enqueues
+ *     forward(c + 1), push(c + 1), combine_peer(c), backward(c)
+ * so the partials of a chunk have been travelling for a whole backward step before anyone waits for them.
+ *
+ * Buffers: one per rank, lce_parts_bytes() bytes, 256-byte aligned, zero before first use, owned by the caller,
+ * addressed through an lce_peer_table (as for the dx exchange; a separate buffer). It holds four slots, selected by
+ * epoch % 4. epoch: a counter the caller increases by one per lce_parts_push on this set of buffers (from 1, same
+ * sequence on all ranks). A push for epoch e must be ordered (stream order on each rank is enough) after that rank's
+ * lce_combine_chunk_peer of epoch e - 2 or later; the four slots then make it impossible to overwrite partials
+ * that some rank has not merged yet.
+ *
+ * lce_parts_push          row_parts_local as written by lce_forward_chunk for rows [row0, row0 + rows).
+ * lce_combine_chunk_peer  lce_combine_chunk reading all ranks' partials of `epoch` from this rank's buffer. When the
+ *                         wait for a flag runs out (wait_ms, <= 0: 10 s) the status word is set and the loss
+ *                         of the pass becomes NaN. */
+int lce_parts_bytes(const lce_problem* p, size_t* bytes);
+int lce_parts_push(const lce_problem* p, const float* row_parts_local, int64_t row0, int64_t rows,
+                   const lce_peer_table* peers, uint32_t epoch, void* stream);
+int lce_combine_chunk_peer(const lce_problem* p, const lce_peer_table* peers, uint32_t epoch, const int64_t* labels,
+                           int64_t row0, int64_t rows, void* workspace, int32_t wait_ms, void* stream);
 
 /* out5: float[5] = loss, z_value, logit_max, logit_entropy, logit_norm (the reference's return
  * tuple, ops.py:802). The last three are only meaningful with monitoring. If any kernel of the pass

@@ -52,7 +52,7 @@ class Problem(ctypes.Structure):
         ("logit_scale", ctypes.c_float),
         ("z_regularization", ctypes.c_float),
         ("slab_mode", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("chunk_buffers", ctypes.c_int32),
     ]
 
 
@@ -136,6 +136,10 @@ SIGNATURES = {
     "lce_begin": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _vp, _vp]),
     "lce_forward_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _vp, _vp]),
     "lce_combine_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _vp, _i64, _i64, _vp, _vp]),
+    "lce_parts_bytes": (ctypes.c_int, [ctypes.POINTER(Problem), ctypes.POINTER(ctypes.c_size_t)]),
+    "lce_parts_push": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _i64, ctypes.POINTER(PeerTable), _u32, _vp]),
+    "lce_combine_chunk_peer": (
+        ctypes.c_int, [ctypes.POINTER(Problem), ctypes.POINTER(PeerTable), _u32, _vp, _i64, _i64, _vp, _i32, _vp]),
     "lce_dz_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _i64, _vp, _vp]),
     "lce_dx_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _vp]),
     "lce_peer_bytes": (ctypes.c_int, [ctypes.POINTER(Problem), _i32, ctypes.POINTER(ctypes.c_size_t)]),

@@ -24,7 +24,7 @@ struct PassScalars {
   float max_logit;   // max over ALL rows and columns of z
   float n_valid;     // number of rows whose label is not ignore_index
   int status;        // device status word, 0 = ok
-  int rescue;        // row-reference mode: set when a row's max logit is more than kRefRange from its reference
+  int unused0;
   int rerun_groups;  // row-reference mode: 256-row groups of this pass whose forward had to be recomputed ...
   int seen_groups;   // ... out of this many (what a caller needs to pick the slab mode of its next pass)
 };
@@ -73,9 +73,14 @@ __device__ __forceinline__ float block_max_float(float v, float* scratch /*[32]*
 }
 
 // One block. Counts labels != ignore_index and resets the accumulators of the pass.
+// rescue_groups / rescue_groups2: the re-run flags of the workspace's one or two sets of per-chunk buffers
+// (n_groups ints each: one per 256-row group, then the "any group flagged" word of the chunk).
 __global__ void begin_kernel(const long long* __restrict__ labels, long long n, long long ignore_index,
-                             PassScalars* sc, int* rescue_groups, int n_groups) {
-  for (int g = threadIdx.x; g < n_groups; g += blockDim.x) rescue_groups[g] = 0;
+                             PassScalars* sc, int* rescue_groups, int* rescue_groups2, int n_groups) {
+  for (int g = threadIdx.x; g < n_groups; g += blockDim.x) {
+    rescue_groups[g] = 0;
+    if (rescue_groups2 != nullptr) rescue_groups2[g] = 0;
+  }
   __shared__ double scratch[32];
   double cnt = 0.0;
   for (long long i = threadIdx.x; i < n; i += blockDim.x) cnt += (labels[i] != ignore_index) ? 1.0 : 0.0;
@@ -88,7 +93,7 @@ __global__ void begin_kernel(const long long* __restrict__ labels, long long n, 
     sc->max_logit = -INFINITY;
     sc->n_valid = (float)total;
     sc->status = 0;
-    sc->rescue = 0;
+    sc->unused0 = 0;
     sc->rerun_groups = 0;
     sc->seen_groups = 0;
   }
@@ -227,23 +232,34 @@ probe_ref_kernel(const float* __restrict__ tile_max, long long stat_ld, int tile
   row_ref[r] = m + kProbeMargin;
 }
 
-// One block of 1024 threads per chunk. parts_all: [world][ROW_PARTS][stat_ld].
-__global__ void __launch_bounds__(1024)
-combine_kernel(const float* __restrict__ parts_all, int world, const long long* __restrict__ labels, int rows,
-               long long stat_ld, long long ignore_index, int monitoring, float* __restrict__ lse_out,
-               PassScalars* sc, int* rescue_groups, int n_groups) {
+// A value that another GPU may have stored while this kernel was already running (published through a flag that
+// this kernel acquired): a plain coherent load, never the read-only path.
+__device__ __forceinline__ float ld_coherent(const float* p) {
+  float v;
+  asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Body of the combine step, for one block of 1024 threads per chunk. parts_all: [world][ROW_PARTS][stat_ld].
+// rescue_groups: n_groups ints of this chunk's buffers; the last one is the chunk's "any group flagged" word.
+template <bool kCoherent>
+__device__ __forceinline__ void combine_rows(const float* parts_all, int world, const long long* __restrict__ labels,
+                                             int rows, long long stat_ld, long long ignore_index, int monitoring,
+                                             float* __restrict__ lse_out, PassScalars* sc, int* rescue_groups,
+                                             int n_groups) {
   __shared__ double scratch_d[32];
   __shared__ float scratch_f[32];
   double a_nll = 0.0, a_lse2 = 0.0, a_ent = 0.0, a_norm = 0.0;
   float a_max = -INFINITY;
+  auto get = [](const float* p) { return kCoherent ? ld_coherent(p) : __ldg(p); };
   for (int r = threadIdx.x; r < rows; r += blockDim.x) {
     float m = -INFINITY, s = 0.f, u = 0.f, t = 0.f, q = 0.f, zmax = -INFINITY;
     for (int g = 0; g < world; ++g) {
       const float* pg = parts_all + (long long)g * ROW_PARTS * stat_ld;
-      lse_merge(m, s, u, pg[0 * stat_ld + r], pg[1 * stat_ld + r], pg[3 * stat_ld + r]);
-      t += pg[2 * stat_ld + r];
-      q += pg[4 * stat_ld + r];
-      zmax = fmaxf(zmax, pg[5 * stat_ld + r]);
+      lse_merge(m, s, u, get(pg + 0 * stat_ld + r), get(pg + 1 * stat_ld + r), get(pg + 3 * stat_ld + r));
+      t += get(pg + 2 * stat_ld + r);
+      q += get(pg + 4 * stat_ld + r);
+      zmax = fmaxf(zmax, get(pg + 5 * stat_ld + r));
     }
     const float lse = m + logf(s);
     lse_out[r] = lse;
@@ -269,14 +285,22 @@ combine_kernel(const float* __restrict__ parts_all, int world, const long long* 
     sc->sum_ent += t_ent;
     sc->sum_norm += t_norm;
     sc->max_logit = fmaxf(sc->max_logit, t_max);
-    sc->rescue = 0;  // the chunk's conditional re-run (if any) is behind us
     int flagged = 0;
-    for (int g = 0; g < n_groups; ++g) flagged += rescue_groups[g] != 0;
+    for (int g = 0; g + 1 < n_groups; ++g) flagged += rescue_groups[g] != 0;
     sc->rerun_groups += flagged;
     sc->seen_groups += (rows + 255) >> 8;
   }
   __syncthreads();
+  // the chunk's conditional re-run (if any) is behind us: clear its flags for the next chunk that uses these buffers
   for (int g = threadIdx.x; g < n_groups; g += blockDim.x) rescue_groups[g] = 0;
+}
+
+__global__ void __launch_bounds__(1024)
+combine_kernel(const float* __restrict__ parts_all, int world, const long long* __restrict__ labels, int rows,
+               long long stat_ld, long long ignore_index, int monitoring, float* __restrict__ lse_out,
+               PassScalars* sc, int* rescue_groups, int n_groups) {
+  combine_rows<false>(parts_all, world, labels, rows, stat_ld, ignore_index, monitoring, lse_out, sc, rescue_groups,
+                      n_groups);
 }
 
 __global__ void finalize_kernel(const PassScalars* sc, double n_rows_total, float z_regularization,

@@ -108,6 +108,49 @@ __device__ __forceinline__ bool peer_wait_all(const uint32_t* flags, int world, 
   return s_fail == 0;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Exchange of the per-row softmax partials (replaces an all-gather). Buffer of one rank:
+//   [ flags: 8 senders, uint32 ] (padded to 1 KiB)   [ 4 slots x [world][ROW_PARTS][chunk_rows] fp32 ]
+// A sender copies its [ROW_PARTS][rows] block into slot (epoch % 4), position `rank`, of EVERY rank's buffer
+// (parts_push_kernel), then peer_signal_kernel publishes flag[rank] = epoch everywhere. The combine step of a rank
+// waits for all flags to reach the epoch and merges the blocks in rank order.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPartsSlots = 4;
+__host__ __device__ inline size_t parts_slot_bytes(int world, long long chunk_rows) {
+  return (size_t(world) * ROW_PARTS * size_t(chunk_rows) * sizeof(float) + 255) / 256 * 256;
+}
+__host__ __device__ inline size_t parts_slot_off(int world, long long chunk_rows, uint32_t epoch) {
+  return kPeerFlagBytes + size_t(epoch % kPartsSlots) * parts_slot_bytes(world, chunk_rows);
+}
+
+// local: [ROW_PARTS][stat_ld] of this rank; rows [row_lo, row_lo + rows) of each of the ROW_PARTS arrays are sent.
+__global__ void __launch_bounds__(256)
+parts_push_kernel(PeerBases peers, int world, int rank, const float* __restrict__ local, long long stat_ld, int row_lo,
+                  int rows, size_t slot_off) {
+  const long long per_peer = (long long)ROW_PARTS * rows;
+  const long long total = per_peer * world;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int g = int(i / per_peer);
+    const long long j = i - (long long)g * per_peer;
+    const int q = int(j / rows);
+    const int r = row_lo + int(j - (long long)q * rows);
+    float* dst = reinterpret_cast<float*>(peers.base[g] + slot_off) + ((long long)rank * ROW_PARTS + q) * stat_ld + r;
+    *dst = local[(long long)q * stat_ld + r];
+  }
+}
+
+// lce_combine_chunk for a sharded run whose partials arrive through the exchange buffer: one block; waits for the
+// flags of all ranks first. On expiry nothing is merged and the status word makes the loss of the pass NaN.
+__global__ void __launch_bounds__(1024)
+combine_peer_kernel(const uint32_t* flags, uint32_t epoch, long long limit_ns, const float* parts_all, int world,
+                    const long long* __restrict__ labels, int rows, long long stat_ld, long long ignore_index,
+                    int monitoring, float* __restrict__ lse_out, PassScalars* sc, int* rescue_groups, int n_groups) {
+  if (!peer_wait_all(flags, world, epoch, limit_ns, &sc->status)) return;
+  combine_rows<true>(parts_all, world, labels, rows, stat_ld, ignore_index, monitoring, lse_out, sc, rescue_groups,
+                     n_groups);
+}
+
 template <typename T>
 struct Pack8;
 template <>

@@ -79,6 +79,25 @@ class NativeBackend:
             "lce_combine_chunk",
         )
 
+    def parts_bytes(self, prob) -> int:
+        out = ctypes.c_size_t(0)
+        _native.check(self.lib.lce_parts_bytes(ctypes.byref(prob), ctypes.byref(out)), "lce_parts_bytes")
+        return int(out.value)
+
+    def parts_push(self, prob, row_parts, row0, rows, table, epoch, stream_of):
+        _native.check(
+            self.lib.lce_parts_push(ctypes.byref(prob), _ptr(row_parts), row0, rows, ctypes.byref(table), epoch,
+                                    self._stream(stream_of)),
+            "lce_parts_push",
+        )
+
+    def combine_chunk_peer(self, prob, table, epoch, y, row0, rows, workspace, wait_ms=0):
+        _native.check(
+            self.lib.lce_combine_chunk_peer(ctypes.byref(prob), ctypes.byref(table), epoch, _ptr(y), row0, rows,
+                                            _ptr(workspace), wait_ms, self._stream(workspace)),
+            "lce_combine_chunk_peer",
+        )
+
     def dz_chunk(self, prob, x, y, row0, rows, workspace):
         _native.check(
             self.lib.lce_dz_chunk(ctypes.byref(prob), _ptr(x), x.stride(0), _ptr(y), row0, rows, _ptr(workspace),
@@ -189,6 +208,12 @@ class ShardSpec:
     peer_exchange(prob, dx_dtype) -> None or an object with ``table`` (a ``_native.PeerTable``), ``next_epoch()``
     and ``wait_ms``: when given, dx is exchanged by the contraction's own stores into peer-mapped memory
     (``lce_dx_chunk_peer`` and friends) and reduce_dx is not called.
+    parts_exchange(prob) -> None or an object with ``table``, ``next_epoch()`` and ``wait_ms``: when given, the row
+    partials travel by stores into peer-mapped memory (``lce_parts_push`` / ``lce_combine_chunk_peer``) instead of
+    gather_row_parts, and the chunks are software-pipelined: the forward of chunk c + 1 is enqueued before the combine
+    and backward steps of chunk c, so nobody waits for partials that have not had a whole backward step to arrive.
+    reduce_dx_once: reduce_dx is called once, with the whole dx, after the last chunk (one collective and one
+    cross-rank synchronisation point per pass) instead of once per chunk with that chunk's rows.
     """
 
     rank: int
@@ -197,6 +222,8 @@ class ShardSpec:
     gather_row_parts: Callable[[torch.Tensor], torch.Tensor]
     reduce_dx: Callable[[torch.Tensor], None]
     peer_exchange: Optional[Callable] = None
+    parts_exchange: Optional[Callable] = None
+    reduce_dx_once: bool = False
 
 
 # A chunk whose row count allows it is processed as this many sub-chunks, so that the memory-bound slab transform
@@ -343,6 +370,13 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     )
     dev = x.device
     n_chunks = -(-N // N_group)
+    # Row partials over peer memory (sharded runs): whether it is used depends only on values that are equal on all
+    # ranks. It comes with software pipelining of the chunks, which needs a second set of per-chunk buffers.
+    parts = None
+    if shard is not None and shard.parts_exchange is not None and not split:
+        parts = shard.parts_exchange(prob)
+        if parts is not None and n_chunks > 1:
+            prob.chunk_buffers = 2
     workspace = torch.empty(backend.workspace_bytes(prob), dtype=torch.uint8, device=dev)
     row_parts = torch.empty(ROW_PARTS * N_group, dtype=torch.float32, device=dev)
     out5 = torch.empty(5, dtype=torch.float32, device=dev)
@@ -370,8 +404,9 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
         return torch.cuda.stream(side)
 
     peer = None
-    if shard is not None and want_dx and shard.peer_exchange is not None:
+    if shard is not None and want_dx and shard.peer_exchange is not None and parts is None:
         peer = shard.peer_exchange(prob, x.dtype)
+    dx_once = shard is not None and shard.reduce_dx_once and peer is None
 
     peer_done = []
     xstream = None
@@ -379,7 +414,32 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
         xstream = _side_stream(dev, "exchange")
 
     backend.begin(prob, y, workspace)
-    for ci, row0 in enumerate(range(0, N, N_group)):
+    chunks = [] if parts is None else [(ci, r0, min(N_group, N - r0)) for ci, r0 in enumerate(range(0, N, N_group))]
+    if parts is not None:
+        # Pipelined order:  F0 P0 | F1 P1 C0 B0 | F2 P2 C1 B1 | ... | C(n-1) B(n-1)   (F forward, P push of the row
+        # partials to all ranks, C wait + combine, B backward). Consecutive chunks use alternate slabs.
+        def forward_and_push(ci, r0, n):
+            backend.forward_chunk(prob, x, At, y, r0, n, workspace, row_parts)
+            epoch = parts.next_epoch()
+            backend.parts_push(prob, row_parts, r0, n, parts.table, epoch, workspace)
+            return epoch
+
+        epochs = {0: forward_and_push(*chunks[0])}
+    for ci, row0, rows in chunks:
+        if ci + 1 < n_chunks:
+            epochs[ci + 1] = forward_and_push(*chunks[ci + 1])
+        backend.combine_chunk_peer(prob, parts.table, epochs.pop(ci), y, row0, rows, workspace, parts.wait_ms)
+        if want_grad:
+            backend.dz_chunk(prob, x, y, row0, rows, workspace)
+            if want_dx:
+                backend.dx_chunk(prob, At, row0, rows, workspace, dx)
+                if not dx_once:
+                    shard.reduce_dx(dx[row0:row0 + rows])
+            if want_dW:
+                last = ci == n_chunks - 1
+                final = None if not last else (dW if dW_acc is None else dW_acc)
+                backend.dw_chunk(prob, x, row0, rows, workspace, dW_acc, ci == 0, final)
+    for ci, row0 in enumerate(range(0, N, N_group) if parts is None else ()):
         rows = min(N_group, N - row0)
         subs = _split_rows(row0, rows, split)
         ready = []
@@ -429,7 +489,7 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
                     peer_done.append(done)
                     continue
                 backend.dx_chunk(prob, At, r0, n, workspace, dx)
-                if shard is not None:
+                if shard is not None and not dx_once:
                     shard.reduce_dx(dx[r0:r0 + n])
             last = ci == n_chunks - 1
             if want_dW:
@@ -439,6 +499,8 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
         main.wait_stream(side)
     if xstream is not None:
         torch.cuda.current_stream(dev).wait_stream(xstream)
+    if dx_once and want_dx:
+        shard.reduce_dx(dx)
     backend.finalize(prob, workspace, out5)
     if native and not per_tile and x.dtype != torch.float16 and os.environ.get("LCE_SLAB_MODE", "auto") == "auto":
         slab_mode_policy.record(policy_key, backend, workspace)

@@ -8,9 +8,13 @@ and ``y`` are replicated. Per row chunk:
 2. ONE small all-gather (``6 * chunk_rows`` floats per rank) makes all partials visible everywhere and a
    local kernel merges them in rank order into the global log-sum-exp -- bitwise identical on every
    rank, which a max/sum all-reduce pair would not guarantee;
+   By default the partials do not even go through a collective: every rank stores them into all ranks'
+   peer-mapped buffers and publishes a flag (``PartsExchange``), and the chunks are software-pipelined -- the
+   forward of chunk c + 1 is enqueued before the combine and backward of chunk c, on two alternating slabs -- so
+   the partials of a chunk have a whole backward step to arrive before anyone waits for them (bounded waits);
 3. every rank forms dZ for its slab, its own dW slab (no communication) and a partial dx, which is
-   summed over the ranks with an all-reduce of the chunk's rows in stream order (16 MiB at the default
-   shape). ``LCE_PEER_DX=1`` selects the device-side exchange instead (``PeerExchange``): the epilogue of
+   summed over the ranks with ONE all-reduce of the whole dx at the end of the pass (``LCE_DX_REDUCE=chunk``:
+   one all-reduce per chunk, of that chunk's rows, in stream order). ``LCE_PEER_DX=1`` selects the device-side exchange instead (``PeerExchange``): the epilogue of
    the dx contraction stores each fp32 output tile into peer-mapped memory of the rank that owns the
    rows, the owner adds the tiles of all ranks in a fixed order, rounds once and stores the finished rows
    back to everyone, on a second stream underneath the next contractions; dx is then bitwise identical
@@ -129,6 +133,68 @@ class PeerExchange:
         return cls._cache[key]
 
 
+class PartsExchange:
+    """Peer-mapped buffers (one per rank, symmetric memory) through which the ranks hand each other the per-row
+    softmax partials of a chunk: every rank stores its partials into all ranks' buffers and publishes a flag
+    (``lce_parts_push``); the combine step waits for the flags with a bounded wait (``lce_combine_chunk_peer``).
+    Replaces the per-chunk all-gather, a cross-rank synchronisation in the middle of every chunk.
+
+    Built collectively on first use for a given size and kept for the life of the process. ``next_epoch`` must
+    advance identically on all ranks, which it does when all ranks run the same sequence of passes.
+    ``LCE_PEER_PARTS=0`` keeps the all-gather."""
+
+    _cache = {}
+    _unavailable = set()
+
+    def __init__(self, group, nbytes: int, device: torch.device):
+        import torch.distributed._symmetric_memory as symm
+
+        pg = group if group is not None else dist.group.WORLD
+        self.buf = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, pg)
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        ptrs = list(self.handle.buffer_ptrs)
+        assert len(ptrs) == world and ptrs[rank] == self.buf.data_ptr()
+        self.table = _native.PeerTable()
+        self.table.world, self.table.rank = world, rank
+        for g in range(world):
+            self.table.base[g] = ptrs[g]
+        self.epoch = 0
+        self.wait_ms = int(os.environ.get("LCE_PEER_WAIT_MS", "0"))
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every rank's flags are zero before anyone signals
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    @classmethod
+    def for_problem(cls, group, prob, device) -> Optional["PartsExchange"]:
+        """The exchange for this problem, or None when the all-gather has to be used. The decision depends only on
+        values that are equal on all ranks."""
+        backend = ops.get_backend()
+        world = dist.get_world_size(group)
+        if (os.environ.get("LCE_PEER_PARTS", "1") == "0" or os.environ.get("LCE_PEER_DX", "0") == "1"
+                or not getattr(backend, "requires_cuda", True) or device.type != "cuda" or world < 2
+                or world > _native.MAX_PEERS):
+            return None
+        gid = id(group) if group is not None else 0
+        if (gid, device.index) in cls._unavailable:
+            return None
+        nbytes = backend.parts_bytes(prob)
+        key = (gid, device.index, nbytes)
+        if key not in cls._cache:
+            try:
+                cls._cache[key] = cls(group, nbytes, device)
+            except (RuntimeError, ImportError, AssertionError) as err:  # no peer mapping between these GPUs
+                cls._unavailable.add((gid, device.index))
+                print(f"linear_cross_entropy_loss_b200: peer exchange of row partials unavailable ({err}); "
+                      f"using all-gather")
+                return None
+        return cls._cache[key]
+
+
 class VocabShardedLinearXent(torch.autograd.Function):
     """Sharded counterpart of ``ops.LinearXentImplementation``: same outputs, W given as this rank's slab."""
 
@@ -144,7 +210,9 @@ class VocabShardedLinearXent(torch.autograd.Function):
             coll = _Collectives(group, world)
             spec = ops.ShardSpec(rank=rank, world=world, vocab_offset=rank * v_local,
                                  gather_row_parts=coll.gather_row_parts, reduce_dx=coll.reduce_dx,
-                                 peer_exchange=lambda prob, dt: PeerExchange.for_problem(group, prob, dt, x.device))
+                                 peer_exchange=lambda prob, dt: PeerExchange.for_problem(group, prob, dt, x.device),
+                                 parts_exchange=lambda prob: PartsExchange.for_problem(group, prob, x.device),
+                                 reduce_dx_once=os.environ.get("LCE_DX_REDUCE", "pass") != "chunk")
             want = (bool(ctx.needs_input_grad[0]), bool(ctx.needs_input_grad[2]))
             with torch.no_grad():
                 out5, dx, dA, _ = ops.run_pass(x, y_flat, A, ignore_index, z_regularization, logit_scale,

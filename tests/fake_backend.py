@@ -51,6 +51,20 @@ class FakeBackend:
         st["zmax"] = max(st["zmax"], float(m.max()))
         st.setdefault("lse", {})[row0] = lse
 
+    # The row-partials exchange over peer memory, for one rank: slots keyed by epoch in the table object.
+    def parts_bytes(self, prob):
+        return 4096
+
+    def parts_push(self, prob, row_parts, row0, rows, table, epoch, stream_of):
+        self.calls.append(("parts_push", epoch))
+        assert len(table.slots) < 4, "four slots: at most four epochs may be unmerged"
+        table.slots[epoch] = row_parts.clone()
+
+    def combine_chunk_peer(self, prob, table, epoch, y, row0, rows, workspace, wait_ms=0):
+        self.calls.append(("combine_chunk_peer", epoch))
+        self.combine_chunk(prob, table.slots.pop(epoch), y, row0, rows, workspace)
+        self.calls.pop()  # the inner combine_chunk entry
+
     def dz_chunk(self, prob, x, y, row0, rows, workspace):
         self.calls.append("dz_chunk")
         st = self.state[workspace.data_ptr()]

@@ -28,9 +28,13 @@ def main():
     for dtype, chunk, cos_min in ((torch.bfloat16, 256, 0.99999), (torch.float16, 1024, 0.999995)):
         x, y, W = random_problem(N, H, V, dtype, seed=0)
         ref = oracle.forward_backward(x, y, W, -1, 1e-4, 0.5)
-        # dx summed by the contraction's own stores into peer-mapped memory, then by an NCCL all-reduce
-        for peer_dx in ("1", "0"):
+        # three data paths: dx summed by the contraction's own stores into peer-mapped memory; the default (row
+        # partials pushed over peer memory, chunks pipelined, ONE all-reduce of dx per pass); the plain collectives
+        # (all-gather of the partials and an all-reduce of dx per chunk)
+        for peer_dx, peer_parts, dx_reduce in (("1", "1", "pass"), ("0", "1", "pass"), ("0", "0", "chunk")):
             os.environ["LCE_PEER_DX"] = peer_dx
+            os.environ["LCE_PEER_PARTS"] = peer_parts
+            os.environ["LCE_DX_REDUCE"] = dx_reduce
             xd = x.cuda().requires_grad_(True)
             Ws = W[:, rank * vl:(rank + 1) * vl].contiguous().cuda().requires_grad_(True)
             for _ in range(2):  # twice: the second pass reuses the exchange buffers with later epochs
@@ -47,8 +51,12 @@ def main():
                 theirs = xd.grad.clone()
                 dist.broadcast(theirs, src=0)
                 good &= torch.equal(theirs, xd.grad)  # bitwise the same dx on every rank
+            if peer_dx == "0" and peer_parts == "1" and dtype == torch.bfloat16:
+                from linear_cross_entropy_loss_b200.sharded import PartsExchange
+                good &= len(PartsExchange._cache) >= 1  # the pipelined path with pushed partials really ran
             if not good:
-                print(f"rank {rank}: mismatch with {dtype}, LCE_PEER_DX={peer_dx}", flush=True)
+                print(f"rank {rank}: mismatch with {dtype}, LCE_PEER_DX={peer_dx} LCE_PEER_PARTS={peer_parts} "
+                      f"LCE_DX_REDUCE={dx_reduce}: loss {out[0].item()} vs {ref.loss}", flush=True)
             ok &= bool(good)
     flag = torch.tensor([1.0 if ok else 0.0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

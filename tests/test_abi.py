@@ -110,7 +110,7 @@ def test_workspace_size_accounts_for_slab_statistics_and_partials(lib):
 @pytest.mark.parametrize("kw,code", [
     (dict(dtype=7), -1), (dict(hidden=0), -1), (dict(logit_scale=0.0), -1), (dict(z_regularization=-1.0), -1),
     (dict(world=0), -1), (dict(n_rows_total=0), -1),
-    (dict(hidden=100), -2), (dict(chunk_rows=192), -2), (dict(slab_mode=5), -1), (dict(reserved=1), -1),
+    (dict(hidden=100), -2), (dict(chunk_rows=192), -2), (dict(slab_mode=5), -1), (dict(chunk_buffers=3), -1),
     (dict(vocab_local=1 << 31), -8),
 ])
 def test_invalid_problems_are_rejected_without_a_device(lib, kw, code):

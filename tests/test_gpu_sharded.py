@@ -121,6 +121,111 @@ def test_emulated_peer_exchange_of_dx_on_one_gpu(world, dtype, N, chunk):
     assert torch.all((got - want).abs() <= eps * want.abs() + 5e-7 * mass + tiny)
 
 
+def _tables(bufs):
+    world = len(bufs)
+    tables = []
+    for g in range(world):
+        t = _native.PeerTable()
+        t.world, t.rank = world, g
+        for k in range(world):
+            t.base[k] = bufs[k].data_ptr()
+        tables.append(t)
+    return tables
+
+
+@pytest.mark.parametrize("world,dtype,N,chunk", [(2, torch.bfloat16, 768, 256), (4, torch.float32, 1280, 256),
+                                                 (8, torch.bfloat16, 600, 256)])
+def test_emulated_pipelined_pass_with_the_row_partials_exchange(world, dtype, N, chunk):
+    """The software-pipelined sharded pass through the C ABI, G ranks emulated on this GPU: forward and push of chunk
+    c + 1 before combine and backward of chunk c, two sets of per-chunk buffers per workspace, row partials stored
+    into every rank's exchange buffer (four slots) instead of an all-gather. Ranks run phase by phase, so every flag
+    a kernel waits for was published by an earlier launch. Checked against the oracle; scalars bitwise equal on all
+    ranks; two passes in a row (epochs continue, slots are reused)."""
+    H, V = 256, 4096
+    x, y, W = random_problem(N, H, V, dtype, seed=20 + world)
+    xd, yd = x.cuda(), y.cuda()
+    vl = V // world
+    slabs = [W[:, g * vl:(g + 1) * vl].contiguous().cuda() for g in range(world)]
+    be = ops.get_backend()
+    probs = [_native.Problem(n_rows_total=N, chunk_rows=chunk, hidden=H, vocab_local=vl, vocab_offset=g * vl,
+                             ignore_index=-1, world=world, dtype=ops._DTYPE_CODE[dtype], monitoring=1, want_grad=1,
+                             logit_scale=0.5, z_regularization=1e-3, chunk_buffers=2) for g in range(world)]
+    one_buffer = _native.Problem(n_rows_total=N, chunk_rows=chunk, hidden=H, vocab_local=vl, vocab_offset=0,
+                                 ignore_index=-1, world=world, dtype=ops._DTYPE_CODE[dtype], monitoring=1, want_grad=1,
+                                 logit_scale=0.5, z_regularization=1e-3)
+    assert be.workspace_bytes(probs[0]) > be.workspace_bytes(one_buffer)  # two sets of per-chunk buffers
+    ws = [torch.empty(be.workspace_bytes(p), dtype=torch.uint8, device="cuda") for p in probs]
+    bufs = [torch.zeros(be.parts_bytes(probs[0]), dtype=torch.uint8, device="cuda") for _ in range(world)]
+    tables = _tables(bufs)
+    local = [torch.empty(6 * chunk, dtype=torch.float32, device="cuda") for _ in range(world)]
+    chunks = [(r0, min(chunk, N - r0)) for r0 in range(0, N, chunk)]
+    epoch = 0
+    ref = oracle.forward_backward(x, y, W, -1, 1e-3, 0.5)
+    for n_pass in range(2):
+        dxs = [torch.zeros(N, H, dtype=torch.float32, device="cuda") for _ in range(world)]
+        dWs = [torch.empty(H, vl, dtype=torch.float32, device="cuda") for _ in range(world)]
+        outs = [torch.empty(5, dtype=torch.float32, device="cuda") for _ in range(world)]
+        for g in range(world):
+            be.begin(probs[g], yd, ws[g])
+
+        def forward_and_push(ci):
+            nonlocal epoch
+            epoch += 1
+            r0, n = chunks[ci]
+            for g in range(world):
+                be.forward_chunk(probs[g], xd, slabs[g], yd, r0, n, ws[g], local[g])
+                be.parts_push(probs[g], local[g], r0, n, tables[g], epoch, ws[g])
+            return epoch
+
+        epochs = {0: forward_and_push(0)}
+        for ci, (r0, n) in enumerate(chunks):
+            if ci + 1 < len(chunks):
+                epochs[ci + 1] = forward_and_push(ci + 1)
+            for g in range(world):
+                be.combine_chunk_peer(probs[g], tables[g], epochs[ci], yd, r0, n, ws[g], 2000)
+                be.dz_chunk(probs[g], xd, yd, r0, n, ws[g])
+                be.dx_chunk(probs[g], slabs[g], r0, n, ws[g], dxs[g])
+                be.dw_chunk(probs[g], xd, r0, n, ws[g], dWs[g], ci == 0, None)
+        for g in range(world):
+            be.finalize(probs[g], ws[g], outs[g])
+        torch.cuda.synchronize()
+        for g in range(world):
+            assert be.read_status(ws[g]) == 0
+            assert torch.equal(outs[g], outs[0]), "every rank must compute bitwise the same scalars"
+        got = outs[0].cpu().numpy()
+        want = np.array([ref.loss, ref.z_value, ref.logit_max, ref.logit_entropy, ref.logit_norm])
+        np.testing.assert_allclose(got, want, rtol=2e-3)
+        assert abs(got[0] - ref.loss) < 10 * TOL[dtype]["loss"] * ref.loss
+        dx = sum(d.double() for d in dxs).cpu().numpy()
+        dW = torch.cat(dWs, dim=1).double().cpu().numpy()
+        assert cosine(dx, ref.dx) > TOL[dtype]["cos"]
+        assert cosine(dW, ref.dW) > TOL[dtype]["cos"]
+
+
+def test_wait_for_row_partials_runs_out_and_reports():
+    """Nobody pushes: the combine step's bounded wait gives up after wait_ms, merges nothing, and the status word
+    turns the loss of the pass into NaN. The kernel returns normally."""
+    be = ops.get_backend()
+    N, H = 256, 256
+    prob = _native.Problem(n_rows_total=N, chunk_rows=256, hidden=H, vocab_local=512, vocab_offset=0, ignore_index=-1,
+                           world=2, dtype=_native.DTYPE_BF16, monitoring=0, want_grad=0, logit_scale=1.0,
+                           z_regularization=0.0)
+    ws = torch.empty(be.workspace_bytes(prob), dtype=torch.uint8, device="cuda")
+    y = torch.zeros(N, dtype=torch.int64, device="cuda")
+    be.begin(prob, y, ws)
+    bufs = [torch.zeros(be.parts_bytes(prob), dtype=torch.uint8, device="cuda") for _ in range(2)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    be.combine_chunk_peer(prob, _tables(bufs)[0], 1, y, 0, N, ws, 200)
+    t1.record()
+    torch.cuda.synchronize()
+    assert 150 < t0.elapsed_time(t1) < 2000
+    assert be.read_status(ws) == -6  # LCE_ERR_DEVICE_TIMEOUT
+    out5 = torch.zeros(5, dtype=torch.float32, device="cuda")
+    be.finalize(prob, ws, out5)
+    assert torch.isnan(out5[0])
+
+
 def test_peer_wait_runs_out_and_reports_instead_of_hanging():
     """A flag that nothing sets: the bounded wait gives up after wait_ms, copies nothing, and the status word turns
     the loss of the pass into NaN. (No fault is provoked: the kernel returns normally.)"""

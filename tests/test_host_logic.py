@@ -237,6 +237,46 @@ def test_peer_exchange_sequencing_in_the_chunk_loop(fake):
     assert asked == []
 
 
+def test_pipelined_chunks_with_the_row_partials_exchange(fake):
+    """With a row-partials exchange in the shard description the loop runs the chunks software-pipelined -- the
+    forward and push of chunk c + 1 before the combine and backward of chunk c, two sets of per-chunk buffers --
+    never calls gather_row_parts, reduces dx once at the end when asked to, and gives the same results."""
+    class Table:
+        slots = {}
+
+    class Exchange:
+        table, wait_ms, epoch = Table(), 0, 7
+
+        def next_epoch(self):
+            self.epoch += 1
+            return self.epoch
+
+    ex = Exchange()
+    gathers, reduces, probs = [], [], []
+    x, y, W = make(N=640, H=256, V=512)
+    want = oracle.forward_backward(x, y, W, -1)
+    shard = ops.ShardSpec(rank=0, world=1, vocab_offset=0, gather_row_parts=gathers.append,
+                          reduce_dx=lambda rows: reduces.append(tuple(rows.shape)),
+                          parts_exchange=lambda prob: (probs.append(prob), ex)[1], reduce_dx_once=True)
+    out5, dx, dW, _ = ops.run_pass(x, y, W, -1, 0.0, 1.0, 256, False, True, shard=shard)
+    assert abs(out5[0].item() - want.loss) < 1e-5
+    assert np.allclose(dx.numpy(), want.dx, atol=2e-7) and np.allclose(dW.numpy(), want.dW, atol=2e-7)
+    assert gathers == [] and reduces == [(640, 256)] and probs[0].chunk_buffers == 2
+    order = [c if isinstance(c, str) else c[0] + str(c[1]) for c in fake.calls
+             if c in ("forward_chunk", "dx_chunk") or isinstance(c, tuple)]
+    assert order == ["forward_chunk", "parts_push8", "forward_chunk", "parts_push9", "combine_chunk_peer8", "dx_chunk",
+                     "forward_chunk", "parts_push10", "combine_chunk_peer9", "dx_chunk", "combine_chunk_peer10",
+                     "dx_chunk"]
+    # forward only: same order without the backward steps; one chunk: nothing to pipeline, one set of buffers
+    fake.calls.clear()
+    ops.run_pass(x, y, W, -1, 0.0, 1.0, 256, False, False, shard=shard)
+    assert [c[0] for c in fake.calls if isinstance(c, tuple)] == ["parts_push", "parts_push", "combine_chunk_peer",
+                                                                  "parts_push", "combine_chunk_peer",
+                                                                  "combine_chunk_peer"]
+    ops.run_pass(x[:256], y[:256], W, -1, 0.0, 1.0, 256, False, True, shard=shard)
+    assert probs[-1].chunk_buffers == 0 and reduces[-1] == (256, 256)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 def test_collective_sequence_of_a_sharded_pass_does_not_depend_on_the_slab_mode(fake, monkeypatch, dtype):
     """Each rank of a sharded run picks its slab mode by itself (own re-run counters, a polled event), so ranks can
