@@ -341,7 +341,12 @@ def config_dict(cfg, n_gpus, args):
         "vocab_sharding": f"{n_gpus} x {cfg.V // n_gpus} columns" if n_gpus > 1 else "none",
         "dx_exchange": ("none" if n_gpus == 1 else
                         "peer stores fused into the dx contraction" if os.environ.get("LCE_PEER_DX") == "1"
-                        else "NCCL all-reduce per chunk, in stream order"),
+                        else "NCCL all-reduce per chunk, in stream order" if os.environ.get("LCE_DX_REDUCE") == "chunk"
+                        else "one NCCL all-reduce of dx per pass"),
+        "row_partials_exchange": ("none" if n_gpus == 1 else
+                                  "NCCL all-gather per chunk" if (os.environ.get("LCE_PEER_PARTS") == "0"
+                                                                  or os.environ.get("LCE_PEER_DX") == "1")
+                                  else "stores into peer memory + flags, chunks software-pipelined on two slabs"),
         "l2": "inputs larger than L2 (the weight alone is >= 512 MiB per GPU); no explicit flush",
         "gemm_variant": "CTA-pair 256x256 tiles",
     }
