@@ -543,7 +543,8 @@ def main():
                 "d2h_bytes_per_step": 4},
         "gpu_launches": launches, "roofline": roofline, "loss": loss_value, "parity": parity,
         "peak_extra_bytes": peak_extra, "peak_budget_bytes": min(cfg.N, cfg.N_chunk_size) * v_local * 4,
-        # the same without the gradients the caller receives and the fp32 dW accumulator (which the reference keeps too)
+        # the same without the gradients the caller receives and the residual array of dW (together what the
+        # reference's fp32 gradient buffers hold)
         "peak_extra_bytes_excl_grads": peak_extra - cfg.N * cfg.H * x.element_size()
         - cfg.H * v_local * (4 if cfg.N > cfg.N_chunk_size else W.element_size()),
     }

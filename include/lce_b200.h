@@ -135,30 +135,29 @@ int lce_combine_chunk(const lce_problem* p, const float* row_parts_all, const in
  *                Needs lce_combine_chunk of the same rows.
  * lce_dx_chunk   dx rows = dZ W^T * logit_scale / n_valid (ops.py:317,332). dx: [n_rows_total, hidden]
  *                with row stride dx_ld and element type dx_dtype (LCE_DTYPE_*).
- * lce_dw_chunk   dW (+)= x^T dZ * logit_scale / n_valid (ops.py:424,443) accumulated in fp32:
- *                dweight_acc float[hidden, vocab_local] (row stride dw_ld) is overwritten when first != 0
- *                and accumulated into otherwise. When dweight_final is non-null this call is the last of
- *                the pass: the finished sum is written there in the element type of x / W (row stride
- *                dwf_ld) and dweight_acc is only read. A pass of a single call (first != 0 and dweight_final
- *                given) needs no dweight_acc at all (may be null).
- *                dweight_final == dweight_acc (the same address) asks for the finished sum to be written OVER the
- *                accumulator, which saves the separate hidden x vocab output buffer while the workspace is still
- *                alive: element (r, j) of the result, in the element type of W (es bytes), then lies at byte
- *                4 * dw_ld * r + 1024 * (j / 256) + es * (j % 256) of dweight_acc, i.e. every 256-column tile keeps
- *                its place and is narrowed inside its own 1024 bytes (a strided view for the caller to compact
- *                after it has released the workspace). dwf_ld is ignored; for fp32 the accumulator is the result.
+ * lce_dw_chunk   dW (+)= x^T dZ * logit_scale / n_valid (ops.py:424,443), summed over the chunks of the pass in
+ *                more precision than the result has. dweight: [hidden, vocab_local] in the element type of
+ *                x / W (row stride dw_ld elements), overwritten by the call with first != 0 and complete after
+ *                the call with last != 0. For the 16-bit types the running sum is carried as the PAIR
+ *                dweight + dweight_residual, both in the element type: each call rounds the new sum to dweight and
+ *                the rounding error to dweight_residual (about 16 significant bits together; the reference
+ *                accumulates fp16 gradients in fp16 and bf16 gradients in an fp32 buffer the size of W, ops.py:
+ *                440-444, 693). dweight_residual: scratch of the same shape and row stride (dwr_ld == dw_ld), only
+ *                meaningful between the calls of one pass; may be null for a pass of a single call (first and
+ *                last) and for fp32, where dweight is its own accumulator. No buffer of hidden x vocab fp32
+ *                values and no conversion pass exist.
  * lce_backward_chunk = the three in sequence. */
 int lce_dz_chunk(const lce_problem* p, const void* x, int64_t x_ld, const int64_t* labels, int64_t row0,
                  int64_t rows, void* workspace, void* stream);
 int lce_dx_chunk(const lce_problem* p, const void* weight, int64_t w_ld, int64_t row0, int64_t rows, void* workspace,
                  void* dx, int64_t dx_ld, int32_t dx_dtype, void* stream);
 int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0, int64_t rows, void* workspace,
-                 float* dweight_acc, int64_t dw_ld, int32_t first, void* dweight_final, int64_t dwf_ld,
+                 void* dweight, int64_t dw_ld, void* dweight_residual, int64_t dwr_ld, int32_t first, int32_t last,
                  void* stream);
 int lce_backward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
                        const int64_t* labels, int64_t row0, int64_t rows, void* workspace, void* dx,
-                       int64_t dx_ld, int32_t dx_dtype, float* dweight_acc, int64_t dw_ld, int32_t first,
-                       void* dweight_final, int64_t dwf_ld, void* stream);
+                       int64_t dx_ld, int32_t dx_dtype, void* dweight, int64_t dw_ld, void* dweight_residual,
+                       int64_t dwr_ld, int32_t first, int32_t last, void* stream);
 
 /* ---- dx exchange between the ranks of a vocabulary-sharded run, over peer-mapped memory -------------------
  * No counterpart in the reference (it has no multi-GPU path). These three calls replace lce_dx_chunk plus the
@@ -198,6 +197,17 @@ int lce_dx_reduce_peer(const lce_problem* p, int64_t row0, int64_t rows, void* w
                        int32_t dx_dtype, uint32_t epoch, int32_t wait_ms, void* stream);
 int lce_dx_finish_peer(const lce_problem* p, int64_t row0, int64_t rows, void* workspace, const lce_peer_table* peers,
                        uint32_t epoch, void* dx, int64_t dx_ld, int32_t dx_dtype, int32_t wait_ms, void* stream);
+
+/* The whole pass of an UNSHARDED problem (world == 1) in one call: lce_begin, then per chunk lce_forward_chunk,
+ * lce_combine_chunk and -- with want_grad -- lce_dz_chunk, lce_dx_chunk (dx != NULL) and lce_dw_chunk
+ * (dweight != NULL), then lce_finalize; everything on `stream`, nothing synchronises. This is the reference's whole
+ * LinearXentImplementation.forward (ops.py:665-802) behind one entry point, and what makes small problems cheap:
+ * their cost is the host time per call, not the kernels. row_parts: LCE_ROW_PARTS * chunk_rows floats of scratch.
+ * dx / dweight: either may be NULL when that gradient is not wanted (not both, with want_grad); dweight_residual as
+ * for lce_dw_chunk (needed for 16-bit types when the pass has more than one chunk). */
+int lce_fused_pass(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
+                   const int64_t* labels, void* workspace, float* row_parts, void* dx, int64_t dx_ld, int32_t dx_dtype,
+                   void* dweight, int64_t dw_ld, void* dweight_residual, int64_t dwr_ld, float* out5, void* stream);
 
 /* ---- row statistics exchange between the ranks of a vocabulary-sharded run, over peer-mapped memory -------
  * No counterpart in the reference (it has no multi-GPU path). These calls replace the all-gather of the per-row

@@ -150,11 +150,16 @@ SIGNATURES = {
     "lce_dx_finish_peer": (
         ctypes.c_int,
         [ctypes.POINTER(Problem), _i64, _i64, _vp, ctypes.POINTER(PeerTable), _u32, _vp, _i64, _i32, _i32, _vp]),
-    "lce_dw_chunk": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i32, _vp, _i64, _vp]),
+    "lce_dw_chunk": (
+        ctypes.c_int, [ctypes.POINTER(Problem), _vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _i64, _i32, _i32, _vp]),
     "lce_backward_chunk": (
         ctypes.c_int,
-        [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _vp, _i64, _i32, _vp, _i64, _i32, _vp,
-         _i64, _vp],
+        [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _vp, _i64, _i32, _vp, _i64, _vp, _i64,
+         _i32, _i32, _vp],
+    ),
+    "lce_fused_pass": (
+        ctypes.c_int,
+        [ctypes.POINTER(Problem), _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _i64, _vp, _i64, _vp, _vp],
     ),
     "lce_finalize": (ctypes.c_int, [ctypes.POINTER(Problem), _vp, _vp, _vp]),
     "lce_grad_scale_cast": (ctypes.c_int, [_vp, _i32, _i64, _vp, _i32, _i64, _i64, _i64, _vp, _vp]),

@@ -81,15 +81,18 @@ struct GemmParams {
   int accumulate;              // 0: out = coef * acc, 1: out += coef * acc
   float out_scale;             // coef = out_scale / (*out_div)   (out_div may be null: coef = out_scale)
   const float* out_div;
-  void* out_final;             // when non-null the result goes here, converted to the input element type,
-  long long out_final_ld;      // instead of back to `out` (last accumulation step of dW)
-  int out_final_inplace;       // 1: the converted result overwrites the accumulator itself: element (r, j) goes to
-                               // byte 4 * out_ld * r + 1024 * (j / 256) + es * (j % 256) of `out` -- the first
-                               // half (16-bit types) of the tile's own row segment, so a thread only overwrites
-                               // accumulator values that it has read before (out_final is ignored)
+  // ---- EPI_F32, 16-bit element types: accumulation across launches as a pair of arrays in the ELEMENT type,
+  // sum = out_sum + out_res with out_sum = round(sum) and out_res = round(sum - out_sum) (about 16 significant
+  // bits, against the 8 or 11 of the result). out_sum is the result itself after the last launch: no fp32
+  // accumulator the size of the output, no conversion pass. `accumulate` = 0 for the first launch; out_res may be
+  // null when nothing follows (last launch: the residual is not written) -- a single launch needs none at all.
+  void* out_sum;
+  void* out_res;
+  long long out_pair_ld;       // elements between rows of out_sum and of out_res
+  int out_pair_last;           // 1: last launch of the accumulation
   int out_rows;                // rows / columns of the output that exist; tiles may hang over both edges
   int out_cols;
-  int out_vector_ok;           // 1: out, out_final and their strides allow 32-byte accesses
+  int out_vector_ok;           // 1: out (or out_sum / out_res) and their strides allow 32-byte accesses
 
   // ---- EPI_FWD: softmax statistics + exp slab
   void* slab;                  // [rows, slab_ld] in the input element type: exp(z - b) with b = the row's reference
@@ -121,8 +124,8 @@ struct GemmParams {
   int run_mask_row0;
 
   // ---- output through shared memory and TMA (the third tensor map of the launch): EPI_FWD slab stores;
-  // EPI_F32 tile stores (accumulate == 0) or reduce-adds at the memory side (accumulate == 1) of plain fp32 output
-  // (no out_final, no peer scatter). The map describes exactly what exists, so TMA clips tiles at the edges.
+  // EPI_F32 tile stores of plain fp32 output that is only written (accumulate == 0, no element-type pair, no peer
+  // scatter). The map describes exactly what exists, so TMA clips tiles at the edges.
   int out_tma;
   int c_row0;                  // row of the map that row 0 of this launch's output corresponds to
   int c_split_rows;            // EPI_F32: rows of the map between the outputs of consecutive K-splits
@@ -226,6 +229,50 @@ __device__ __forceinline__ void store_slab_chunk(float* dst, const float (&e)[32
   }
 }
 
+// 32 consecutive 16-bit elements (64 bytes, 32-byte aligned) as floats.
+__device__ __forceinline__ void load_elems32(const __nv_bfloat16* src, float (&f)[32]) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint32_t v[8];
+    ld_global_256(src + 16 * i, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      f[16 * i + 2 * k] = __uint_as_float(v[k] << 16);
+      f[16 * i + 2 * k + 1] = __uint_as_float(v[k] & 0xffff0000u);
+    }
+  }
+}
+__device__ __forceinline__ void load_elems32(const __half* src, float (&f)[32]) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint32_t v[8];
+    ld_global_256(src + 16 * i, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&v[k]));
+      f[16 * i + 2 * k] = t.x;
+      f[16 * i + 2 * k + 1] = t.y;
+    }
+  }
+}
+__device__ __forceinline__ void load_elems32(const float* src, float (&f)[32]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t v[8];
+    ld_global_256(src + 8 * i, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[8 * i + k] = __uint_as_float(v[k]);
+  }
+}
+template <typename T>
+__device__ __forceinline__ float elem_to_float(T v);
+template <>
+__device__ __forceinline__ float elem_to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float elem_to_float<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float elem_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
 // One epilogue warp's pair of staging buffers. Lane l owns row l of the 32-row box: it writes its 128 bytes as eight
 // 16-byte pieces (piece j lands at j ^ (l & 7), the 128-byte swizzle TMA expects), then lane 0 issues the store.
 struct WarpStage {
@@ -243,16 +290,12 @@ struct WarpStage {
                                              uint32_t d) {
     st_shared_128(buf + lane * 128 + ((piece ^ (lane & 7)) << 4), a, b, c, d);
   }
-  // Box (c0 = first column, c1 = first row) of the tensor map; reduce: global += box instead of global = box.
-  __device__ __forceinline__ void commit(const CUtensorMap* tm, const uint8_t* buf, int lane, int c0, int c1,
-                                         bool reduce) {
+  // Stores the box whose first column is c0 and first row c1 of the tensor map.
+  __device__ __forceinline__ void commit(const CUtensorMap* tm, const uint8_t* buf, int lane, int c0, int c1) {
     fence_proxy_async_smem();  // the generic-proxy writes above become visible to the TMA unit
     __syncwarp();
     if (lane == 0) {
-      if (reduce)
-        tma_reduce_add_2d(tm, buf, c0, c1);
-      else
-        tma_store_2d(tm, buf, c0, c1);
+      tma_store_2d(tm, buf, c0, c1);
       bulk_commit_group();
     }
     ++fills;
@@ -307,7 +350,7 @@ __device__ __forceinline__ void slab_chunk_via_tma(const GemmParams& p, const CU
   constexpr bool kHalves = sizeof(Elem) == 2;
   if (!kHalves || (c & 1) == 0) buf = stage.acquire(lane);
   stage_slab_chunk(static_cast<Elem*>(nullptr), buf, lane, c & 1, e);
-  if (!kHalves || (c & 1) == 1) stage.commit(tmC, buf, lane, col0 + (kHalves ? (c - 1) : c) * 32, row0, false);
+  if (!kHalves || (c & 1) == 1) stage.commit(tmC, buf, lane, col0 + (kHalves ? (c - 1) : c) * 32, row0);
 }
 
 // Forward epilogue. For its row i and this tile's 256 columns j (z = scale * acc):
@@ -491,8 +534,9 @@ __device__ __forceinline__ void epilogue_forward(const GemmParams& p, const CUte
     epilogue_forward_tilemax<kKind, kMonitor>(p, tmC, stage, taddr, m_blk, n_blk, row_in_tile);
 }
 
-// Plain fp32 epilogue: result = coef * acc (+ out[split][row, col] when accumulating); the result is stored
-// to out, or -- converted to the input element type -- to out_final when that is given.
+// Plain fp32 epilogue: result = coef * acc (+ what earlier launches accumulated). It goes to the fp32 array `out`
+// (directly, through TMA, or scattered to peers), or -- out_sum given -- into the (sum, residual) pair of arrays in
+// the input element type (see GemmParams).
 template <int kKind>
 __device__ __forceinline__ void epilogue_f32(const GemmParams& p, const CUtensorMap* tmC, WarpStage& stage,
                                              uint32_t taddr, int m_blk, int n_blk, int split, int row_in_tile) {
@@ -510,10 +554,10 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, const CUtensor
   } else {
     dst = p.out + (long long)split * p.out_split_stride + row * p.out_ld + (long long)n_blk * BLOCK_N;
   }
-  Elem* dst_final = p.out_final_inplace
-                        ? reinterpret_cast<Elem*>(dst)
-                        : reinterpret_cast<Elem*>(p.out_final) + row * p.out_final_ld + (long long)n_blk * BLOCK_N;
-  const bool to_final = p.out_final_inplace || p.out_final != nullptr;
+  const bool pair = p.out_sum != nullptr;
+  Elem* dst_sum = reinterpret_cast<Elem*>(p.out_sum) + row * p.out_pair_ld + (long long)n_blk * BLOCK_N;
+  Elem* dst_res = reinterpret_cast<Elem*>(p.out_res) + row * p.out_pair_ld + (long long)n_blk * BLOCK_N;
+  const bool write_res = pair && p.out_res != nullptr && !p.out_pair_last;
   float coef = (p.out_div != nullptr) ? p.out_scale / __ldg(p.out_div) : p.out_scale;
   if (p.row_coef != nullptr) coef *= p.row_coef[row];  // row_coef covers the padded rows too
 #pragma unroll 1
@@ -524,15 +568,15 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, const CUtensor
     const int lim = ncols - c * 32;
     float r[32];
     if (p.out_tma) {
-      // plain fp32 output: this warp's 32 rows x 32 columns go through shared memory and one TMA store (or one
-      // reduce-add, performed at the memory side, when accumulating); TMA drops what lies outside the output
+      // plain fp32 output that is only written: this warp's 32 rows x 32 columns go through shared memory and one
+      // TMA store; TMA drops what lies outside the output
 #pragma unroll
       for (int i = 0; i < 32; ++i) r[i] = coef * __uint_as_float(v[i]);
       const int lane = row_in_tile & 31;
       uint8_t* buf = stage.acquire(lane);
       stage_slab_chunk(static_cast<float*>(nullptr), buf, lane, 0, r);
       stage.commit(tmC, buf, lane, n_blk * BLOCK_N + c * 32,
-                   p.c_row0 + split * p.c_split_rows + m_blk * BLOCK_M + (row_in_tile & ~31), p.accumulate != 0);
+                   p.c_row0 + split * p.c_split_rows + m_blk * BLOCK_M + (row_in_tile & ~31));
     } else if (p.peer_rows_own > 0) {
       // Scatter to the owning rank (whole padded tiles, so no masks). A thread holds 128 contiguous bytes of
       // ITS row, and storing them as they are gives 32 separate 32-byte segments per warp instruction, which a
@@ -570,6 +614,37 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, const CUtensor
       }
     } else if (!row_ok || lim <= 0) {
       // nothing of this chunk exists in the output
+    } else if (pair && lim >= 32 && p.out_vector_ok) {
+      // running sum and residual in the element type: sum = hi + lo + coef * acc; hi' = round(sum), lo' = round(sum - hi')
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] = coef * __uint_as_float(v[i]);
+      if (p.accumulate) {
+        float t[32];
+        load_elems32(dst_sum + c * 32, t);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] += t[i];
+        load_elems32(dst_res + c * 32, t);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] += t[i];
+      }
+      store_slab_chunk(dst_sum + c * 32, r);
+      if (write_res) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] -= elem_to_float<Elem>(cast_elem<Elem>(r[i]));
+        store_slab_chunk(dst_res + c * 32, r);
+      }
+    } else if (pair) {
+      // edge of the output, or rows that are not 32-byte aligned: element by element
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (i < lim) {
+          float val = coef * __uint_as_float(v[i]);
+          if (p.accumulate) val += elem_to_float<Elem>(dst_sum[c * 32 + i]) + elem_to_float<Elem>(dst_res[c * 32 + i]);
+          const Elem hi = cast_elem<Elem>(val);
+          dst_sum[c * 32 + i] = hi;
+          if (write_res) dst_res[c * 32 + i] = cast_elem<Elem>(val - elem_to_float<Elem>(hi));
+        }
+      }
     } else if (lim >= 32 && p.out_vector_ok) {
       // whole chunk inside the output and 32-byte accesses allowed
       if (p.accumulate) {
@@ -585,10 +660,7 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, const CUtensor
 #pragma unroll
         for (int i = 0; i < 32; ++i) r[i] = coef * __uint_as_float(v[i]);
       }
-      if (to_final)
-        store_slab_chunk(dst_final + c * 32, r);
-      else
-        store_slab_chunk(dst + c * 32, r);
+      store_slab_chunk(dst + c * 32, r);
     } else {
       // edge of the output, or an unaligned output: element by element
 #pragma unroll
@@ -596,10 +668,7 @@ __device__ __forceinline__ void epilogue_f32(const GemmParams& p, const CUtensor
         if (i < lim) {
           float val = coef * __uint_as_float(v[i]);
           if (p.accumulate) val += dst[c * 32 + i];
-          if (to_final)
-            dst_final[c * 32 + i] = cast_elem<Elem>(val);
-          else
-            dst[c * 32 + i] = val;
+          dst[c * 32 + i] = val;
         }
       }
     }

@@ -510,7 +510,9 @@ int lce_forward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const v
   // statistics kernel reports it through the device flag `rescue`), the same two kernels again with
   // reference = row max. That second pair returns at once when the flag is clear.
   int* rescue = w.rescue_flag;
-  const bool probe = gp.n_tiles > 2 * kProbeTiles;  // tiny vocabularies: reference 0, the re-run covers the rest
+  // Small vocabularies (below 64 tiles = 16384 columns) skip the probe: reference 0, and the conditional re-run --
+  // cheap at that size -- covers rows whose logits lie outside the window; two launches fewer per chunk.
+  const bool probe = gp.n_tiles >= 64;
   if (probe) {
     GemmParams pp = gp;
     pp.n_tiles = kProbeTiles;
@@ -954,27 +956,26 @@ int lce_dx_finish_peer(const lce_problem* p, int64_t row0, int64_t rows, void* w
 }
 
 int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0, int64_t rows, void* workspace,
-                 float* dweight_acc, int64_t dw_ld, int32_t first, void* dweight_final, int64_t dwf_ld,
+                 void* dweight, int64_t dw_ld, void* dweight_residual, int64_t dwr_ld, int32_t first, int32_t last,
                  void* stream) {
   int v = validate_problem(p);
   if (v != LCE_OK) return v;
   if ((v = check_chunk(p, row0, rows)) != LCE_OK) return v;
-  if (!p->want_grad || !x || !workspace) return LCE_ERR_INVALID_ARGUMENT;
-  if (x_ld < p->hidden) return LCE_ERR_INVALID_ARGUMENT;
-  // the fp32 accumulator is needed unless this single call both starts and finishes the accumulation
-  // dweight_final == dweight_acc: the finished sum overwrites the accumulator in W's element type (tile-gapped layout)
-  const bool inplace = dweight_final != nullptr && dweight_final == static_cast<void*>(dweight_acc);
-  const bool need_acc = !(first && dweight_final != nullptr) || inplace;
-  if (need_acc && (!dweight_acc || dw_ld < p->vocab_local)) return LCE_ERR_INVALID_ARGUMENT;
-  if (dweight_final && !inplace && dwf_ld < p->vocab_local) return LCE_ERR_INVALID_ARGUMENT;
-  if (dweight_acc && (reinterpret_cast<uintptr_t>(dweight_acc) & 3u) != 0) return LCE_ERR_MISALIGNED;
-  if (dweight_final && (reinterpret_cast<uintptr_t>(dweight_final) & (uintptr_t)(elem_size(p->dtype) - 1)) != 0)
+  if (!p->want_grad || !x || !workspace || !dweight) return LCE_ERR_INVALID_ARGUMENT;
+  if (x_ld < p->hidden || dw_ld < p->vocab_local) return LCE_ERR_INVALID_ARGUMENT;
+  const int es = elem_size(p->dtype);
+  // 16-bit types carry the sum over the chunks as dweight + dweight_residual; a pass of one call needs no residual,
+  // and an fp32 dweight is its own accumulator
+  const bool sum_pair = p->dtype != LCE_DTYPE_F32;
+  const bool need_res = sum_pair && !(first && last);
+  if (need_res && (!dweight_residual || dwr_ld != dw_ld)) return LCE_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(dweight) & (uintptr_t)(es - 1)) != 0 ||
+      (need_res && (reinterpret_cast<uintptr_t>(dweight_residual) & (uintptr_t)(es - 1)) != 0))
     return LCE_ERR_MISALIGNED;
   int sms = 0;
   if ((v = ensure_device(&sms)) != LCE_OK) return v;
   cudaStream_t st = (cudaStream_t)stream;
   const Workspace w = layout_workspace(p, workspace, sms, chunk_buffer_of(p, row0));
-  const int es = elem_size(p->dtype);
   const long long local0 = row0 % p->chunk_rows;
 
   // dW (+)= x^T * dZ, scaled by logit_scale / n_valid
@@ -990,7 +991,7 @@ int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0
   if (v != LCE_OK) return v;
   if ((v = make_operand_tmap(&tb, p->dtype, true, w.slab, v_pad, p->chunk_rows, v_pad, rows_of_b_tile(pair))) != LCE_OK)
     return v;
-  // 32-byte epilogue accesses need 32-byte aligned rows in both outputs; otherwise the epilogue goes element-wise
+  // 32-byte epilogue accesses need 32-byte aligned rows in the outputs; otherwise the epilogue goes element-wise
   auto rows_aligned32 = [](const void* ptr, long long ld_bytes) {
     return ptr == nullptr || ((reinterpret_cast<uintptr_t>(ptr) & 31u) == 0 && (ld_bytes & 31) == 0);
   };
@@ -1003,32 +1004,30 @@ int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0
   gp.out_rows = (int)p->hidden;
   gp.out_cols = (int)p->vocab_local;
   gp.out_vector_ok =
-      (rows_aligned32(dweight_acc, dw_ld * 4) && (inplace || rows_aligned32(dweight_final, dwf_ld * es))) ? 1 : 0;
+      (rows_aligned32(dweight, dw_ld * es) && rows_aligned32(need_res ? dweight_residual : nullptr, dw_ld * es)) ? 1 : 0;
   gp.a_k0 = (int)(rowref ? local0 : row0);
   gp.b_k0 = (int)local0;
-  gp.out = dweight_acc;
-  gp.out_ld = dw_ld;
-  gp.out_split_stride = 0;
   gp.accumulate = first ? 0 : 1;
   gp.out_scale = p->logit_scale;
   gp.out_div = &w.scalars->n_valid;
-  gp.out_final = inplace ? nullptr : dweight_final;
-  gp.out_final_ld = dwf_ld;
-  gp.out_final_inplace = (inplace && p->dtype != LCE_DTYPE_F32) ? 1 : 0;  // fp32: the accumulator IS the result
   gp.status = &w.scalars->status;
-  // The first chunk, which only writes the fp32 accumulator, does it through shared memory and TMA tile stores.
-  // The chunks that add to it read-add-store in the epilogue: TMA reduce-adds (performed at the memory side) were
-  // measured 3 % slower for this kernel (1264 against 1300 TFLOP/s at 4096 x 2048 x 131072), LCE_DW_REDUCE=tma
-  // selects them for A/B measurements; the chunk that converts to W's type needs the sum in registers anyway.
-  static const bool reduce_by_tma = [] {
-    const char* e = std::getenv("LCE_DW_REDUCE");
-    return e != nullptr && std::strcmp(e, "tma") == 0;
-  }();
   CUtensorMap tc = ta;
-  if (dweight_final == nullptr && (first || reduce_by_tma) && epilogue_tma_enabled() &&
-      (reinterpret_cast<uintptr_t>(dweight_acc) & 15u) == 0 && ((dw_ld * 4) & 15) == 0) {
-    if ((v = make_store_tmap(&tc, LCE_DTYPE_F32, dweight_acc, p->vocab_local, p->hidden, dw_ld)) != LCE_OK) return v;
-    gp.out_tma = 1;
+  if (sum_pair) {
+    gp.out_sum = dweight;
+    gp.out_res = need_res ? dweight_residual : nullptr;
+    gp.out_pair_ld = dw_ld;
+    gp.out_pair_last = last ? 1 : 0;
+  } else {
+    gp.out = reinterpret_cast<float*>(dweight);
+    gp.out_ld = dw_ld;
+    // A chunk that only writes the fp32 result does it through shared memory and TMA tile stores. Chunks that add
+    // to it read-add-store in the epilogue: TMA reduce-adds (performed at the memory side) were measured 3 % slower
+    // for this kernel (1264 against 1300 TFLOP/s at 4096 x 2048 x 131072).
+    if (first && epilogue_tma_enabled() && (reinterpret_cast<uintptr_t>(dweight) & 15u) == 0 &&
+        ((dw_ld * 4) & 15) == 0) {
+      if ((v = make_store_tmap(&tc, LCE_DTYPE_F32, dweight, p->vocab_local, p->hidden, dw_ld)) != LCE_OK) return v;
+      gp.out_tma = 1;
+    }
   }
   {
     ProfScope prof(PROF_DW, st);
@@ -1039,12 +1038,40 @@ int lce_dw_chunk(const lce_problem* p, const void* x, int64_t x_ld, int64_t row0
 
 int lce_backward_chunk(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
                        const int64_t* labels, int64_t row0, int64_t rows, void* workspace, void* dx, int64_t dx_ld,
-                       int32_t dx_dtype, float* dweight_acc, int64_t dw_ld, int32_t first, void* dweight_final,
-                       int64_t dwf_ld, void* stream) {
+                       int32_t dx_dtype, void* dweight, int64_t dw_ld, void* dweight_residual, int64_t dwr_ld,
+                       int32_t first, int32_t last, void* stream) {
   int v = lce_dz_chunk(p, x, x_ld, labels, row0, rows, workspace, stream);
   if (v != LCE_OK) return v;
   if ((v = lce_dx_chunk(p, weight, w_ld, row0, rows, workspace, dx, dx_ld, dx_dtype, stream)) != LCE_OK) return v;
-  return lce_dw_chunk(p, x, x_ld, row0, rows, workspace, dweight_acc, dw_ld, first, dweight_final, dwf_ld, stream);
+  return lce_dw_chunk(p, x, x_ld, row0, rows, workspace, dweight, dw_ld, dweight_residual, dwr_ld, first, last,
+                      stream);
+}
+
+int lce_fused_pass(const lce_problem* p, const void* x, int64_t x_ld, const void* weight, int64_t w_ld,
+                   const int64_t* labels, void* workspace, float* row_parts, void* dx, int64_t dx_ld, int32_t dx_dtype,
+                   void* dweight, int64_t dw_ld, void* dweight_residual, int64_t dwr_ld, float* out5, void* stream) {
+  int v = validate_problem(p);
+  if (v != LCE_OK) return v;
+  if (p->world != 1 || p->vocab_offset != 0) return LCE_ERR_INVALID_ARGUMENT;  // sharded callers exchange between the steps
+  if (!x || !weight || !labels || !workspace || !row_parts || !out5) return LCE_ERR_INVALID_ARGUMENT;
+  if (!p->want_grad && (dx || dweight)) return LCE_ERR_INVALID_ARGUMENT;
+  if (p->want_grad && !dx && !dweight) return LCE_ERR_INVALID_ARGUMENT;
+  if ((v = lce_begin(p, labels, workspace, stream)) != LCE_OK) return v;
+  const int64_t n_chunks = (p->n_rows_total + p->chunk_rows - 1) / p->chunk_rows;
+  for (int64_t ci = 0; ci < n_chunks; ++ci) {
+    const int64_t row0 = ci * p->chunk_rows;
+    const int64_t rows = std::min<int64_t>(p->chunk_rows, p->n_rows_total - row0);
+    if ((v = lce_forward_chunk(p, x, x_ld, weight, w_ld, labels, row0, rows, workspace, row_parts, stream)) != LCE_OK)
+      return v;
+    if ((v = lce_combine_chunk(p, row_parts, labels, row0, rows, workspace, stream)) != LCE_OK) return v;
+    if (!p->want_grad) continue;
+    if ((v = lce_dz_chunk(p, x, x_ld, labels, row0, rows, workspace, stream)) != LCE_OK) return v;
+    if (dx && (v = lce_dx_chunk(p, weight, w_ld, row0, rows, workspace, dx, dx_ld, dx_dtype, stream)) != LCE_OK) return v;
+    if (dweight && (v = lce_dw_chunk(p, x, x_ld, row0, rows, workspace, dweight, dw_ld, dweight_residual, dwr_ld,
+                                     ci == 0, ci == n_chunks - 1, stream)) != LCE_OK)
+      return v;
+  }
+  return lce_finalize(p, workspace, out5, stream);
 }
 
 int lce_finalize(const lce_problem* p, void* workspace, float* out5, void* stream) {

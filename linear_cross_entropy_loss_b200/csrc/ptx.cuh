@@ -145,12 +145,6 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void
                "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
                : "memory");
 }
-// Same, but global += tile (element-wise add performed at the memory side; the tensor map gives the type).
-__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tmap, const void* smem_src, int c0, int c1) {
-  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
-               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
-               : "memory");
-}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until at most N of this thread's bulk groups still READ their shared-memory source.
 template <int N>

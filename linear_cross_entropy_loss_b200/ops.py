@@ -147,14 +147,25 @@ class NativeBackend:
             "lce_dx_finish_peer",
         )
 
-    def dw_chunk(self, prob, x, row0, rows, workspace, dW_acc, first, dW_final):
+    def dw_chunk(self, prob, x, row0, rows, workspace, dW, dW_res, first, last):
         _native.check(
             self.lib.lce_dw_chunk(
-                ctypes.byref(prob), _ptr(x), x.stride(0), row0, rows, _ptr(workspace), _ptr(dW_acc),
-                0 if dW_acc is None else dW_acc.stride(0), 1 if first else 0, _ptr(dW_final),
-                0 if dW_final is None else dW_final.stride(0), self._stream(workspace),
+                ctypes.byref(prob), _ptr(x), x.stride(0), row0, rows, _ptr(workspace), _ptr(dW), dW.stride(0),
+                _ptr(dW_res), 0 if dW_res is None else dW_res.stride(0), 1 if first else 0, 1 if last else 0,
+                self._stream(workspace),
             ),
             "lce_dw_chunk",
+        )
+
+    def fused_pass(self, prob, x, At, y, workspace, row_parts, dx, dW, dW_res, out5):
+        _native.check(
+            self.lib.lce_fused_pass(
+                ctypes.byref(prob), _ptr(x), x.stride(0), _ptr(At), At.stride(0), _ptr(y), _ptr(workspace),
+                _ptr(row_parts), _ptr(dx), 0 if dx is None else dx.stride(0), _DTYPE_CODE[x.dtype], _ptr(dW),
+                0 if dW is None else dW.stride(0), _ptr(dW_res), 0 if dW_res is None else dW_res.stride(0),
+                _ptr(out5), self._stream(workspace),
+            ),
+            "lce_fused_pass",
         )
 
     def finalize(self, prob, workspace, out5):
@@ -323,13 +334,12 @@ slab_mode_policy = SlabModePolicy()
 
 
 def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size, monitoring, want_grad,
-             shard: Optional[ShardSpec] = None, keep_workspace: bool = False):
+             shard: Optional[ShardSpec] = None):
     """One forward(+gradient) pass over all row chunks.
 
     x: (N, H) with unit inner stride, y: (N,) int64 contiguous, At: (H, V_local) with unit inner stride.
     Returns (out5, dx, dW, workspace): out5 = float32[5] (loss, z_value, logit_max, logit_entropy,
-    logit_norm); dx (N, H) and dW (H, V_local) in the dtype of x / At, or None without want_grad; the workspace
-    only with ``keep_workspace`` (tests read the device status word from it), else None.
+    logit_norm); dx (N, H) and dW (H, V_local) in the dtype of x / At, or None without want_grad.
     Follows the chunk loop of the reference (ops.py:721-791): per chunk forward, [all-gather of the row
     partials,] log-sum-exp combine, dZ preparation, dx, dW accumulation. For fp16 -- whose dZ preparation is a
     pass over the whole slab -- a chunk runs as two sub-chunks and the combine + slab pass of one sub-chunk go
@@ -351,9 +361,21 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     assert x.dtype in _DTYPE_CODE, f"unsupported dtype {x.dtype}"
     assert y.dtype == torch.int64, "labels must be int64"
     assert N >= 1, "x must have at least one row"
-    assert H % 8 == 0, "the hidden size must be divisible by 8"
     assert logit_scale > 0 and z_regularization >= 0
     assert int(N_chunk_size) >= 1
+    if H % 8 != 0:
+        # The kernels move rows of x in 16-byte units. A hidden size that is not a multiple of 8 runs on copies
+        # padded with zero columns of x and zero rows of the weight: the logits do not change, and the gradients of
+        # the padding are dropped again (they are zero columns of dx and unused rows of dW).
+        H8 = -(-H // 8) * 8
+        x_pad = x.new_zeros((N, H8))
+        x_pad[:, :H] = x
+        A_pad = _aligned_rows_like((H8, V), At.dtype, At.device)
+        A_pad[:H] = At
+        A_pad[H:] = 0
+        out5, dx, dW, workspace = run_pass(x_pad, y, A_pad, ignore_index, z_regularization, logit_scale, N_chunk_size,
+                                           monitoring, (want_dx, want_dW), shard)
+        return out5, (None if dx is None else dx[:, :H]), (None if dW is None else dW[:H]), workspace
     # rows per chunk as in the reference (ops.py:687), rounded up to the 128-row tile of the kernels
     N_group = -(-min(N, int(N_chunk_size)) // 128) * 128
 
@@ -380,20 +402,19 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     workspace = torch.empty(backend.workspace_bytes(prob), dtype=torch.uint8, device=dev)
     row_parts = torch.empty(ROW_PARTS * N_group, dtype=torch.float32, device=dev)
     out5 = torch.empty(5, dtype=torch.float32, device=dev)
-    dx = dW = dW_acc = None
+    dx = dW = dW_res = None
     if want_dx:
         dx = torch.empty((N, H), dtype=x.dtype, device=dev)
     if want_dW:
-        if n_chunks > 1:
-            # fp32 accumulator across chunks. The last chunk narrows it IN PLACE to W's element type (every 256-column
-            # tile inside its own bytes), so that no second (H, V) buffer is alive together with the workspace; the
-            # narrowed tiles are compacted into dW once the workspace has been released (see the end of the pass).
-            dW_acc = _aligned_rows_like((H, V), torch.float32, dev)
-        else:
-            dW = _aligned_rows_like((H, V), At.dtype, dev)
+        dW = _aligned_rows_like((H, V), At.dtype, dev)
+        if n_chunks > 1 and At.dtype != torch.float32:
+            # Across chunks the 16-bit gradient is carried as dW + dW_res (the rounding error of dW, in the same
+            # type): about 16 significant bits, no fp32 buffer the size of W, and dW is complete after the last chunk.
+            dW_res = _aligned_rows_like((H, V), At.dtype, dev)
 
     # second stream only where sub-chunks exist (per-tile slabs); everything else runs in order on the caller's stream
-    use_side = native and dev.type == "cuda" and split and SUBCHUNKS == 2
+    use_side = (native and dev.type == "cuda" and split and SUBCHUNKS == 2
+                and len(_split_rows(0, N_group, True)) > 1)  # chunks too small to halve run on one stream
     main = torch.cuda.current_stream(dev) if use_side else None
     side = _side_stream(dev) if use_side else None
 
@@ -413,6 +434,13 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     if peer is not None and getattr(peer, "overlap", False):
         xstream = _side_stream(dev, "exchange")
 
+    if shard is None and not use_side and hasattr(backend, "fused_pass"):
+        # unsharded, one stream: the whole pass is ONE call into the library (same kernels, same order as the loop
+        # below; what it saves is host time per call, which is all that small problems cost)
+        backend.fused_pass(prob, x, At, y, workspace, row_parts, dx, dW, dW_res, out5)
+        if native and not per_tile and x.dtype != torch.float16 and os.environ.get("LCE_SLAB_MODE", "auto") == "auto":
+            slab_mode_policy.record(policy_key, backend, workspace)
+        return out5, dx, dW, workspace
     backend.begin(prob, y, workspace)
     chunks = [] if parts is None else [(ci, r0, min(N_group, N - r0)) for ci, r0 in enumerate(range(0, N, N_group))]
     if parts is not None:
@@ -436,9 +464,7 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
                 if not dx_once:
                     shard.reduce_dx(dx[row0:row0 + rows])
             if want_dW:
-                last = ci == n_chunks - 1
-                final = None if not last else (dW if dW_acc is None else dW_acc)
-                backend.dw_chunk(prob, x, row0, rows, workspace, dW_acc, ci == 0, final)
+                backend.dw_chunk(prob, x, row0, rows, workspace, dW, dW_res, ci == 0, ci == n_chunks - 1)
     for ci, row0 in enumerate(range(0, N, N_group) if parts is None else ()):
         rows = min(N_group, N - row0)
         subs = _split_rows(row0, rows, split)
@@ -491,10 +517,8 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
                 backend.dx_chunk(prob, At, r0, n, workspace, dx)
                 if shard is not None and not dx_once:
                     shard.reduce_dx(dx[r0:r0 + n])
-            last = ci == n_chunks - 1
             if want_dW:
-                final = None if not last else (dW if dW_acc is None else dW_acc)
-                backend.dw_chunk(prob, x, row0, rows, workspace, dW_acc, ci == 0, final)
+                backend.dw_chunk(prob, x, row0, rows, workspace, dW, dW_res, ci == 0, ci == n_chunks - 1)
     if side is not None:
         main.wait_stream(side)
     if xstream is not None:
@@ -504,45 +528,7 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     backend.finalize(prob, workspace, out5)
     if native and not per_tile and x.dtype != torch.float16 and os.environ.get("LCE_SLAB_MODE", "auto") == "auto":
         slab_mode_policy.record(policy_key, backend, workspace)
-    if dW_acc is not None:
-        if not keep_workspace:
-            workspace = None  # released before dW is allocated: stream order makes the reuse of its memory safe
-        dW = _compact_narrowed(dW_acc, At.dtype, V)
-    return out5, dx, dW, (workspace if keep_workspace else None)
-
-
-def _narrowed_tiles(acc: torch.Tensor, dtype, V: int):
-    """Views of an fp32 accumulator (H, V) whose last chunk was narrowed in place (``lce_dw_chunk`` with
-    dweight_final == dweight_acc): [(view of the narrowed values, first column, end column), ...]. Each 256-column
-    tile keeps its 1024 bytes per row and holds its values, in ``dtype``, at the start of them."""
-    H = acc.shape[0]
-    base = acc if acc.is_contiguous() else acc._base  # rows padded to 8 columns: the tiles live in the padded buffer
-    per = 4 // dtype.itemsize  # narrow elements per fp32 slot
-    narrow = base.view(dtype)  # (H, per * ld)
-    full = V // 256
-    out = []
-    if full:
-        tiles = narrow[:, :full * 256 * per].view(H, full, 256 * per)[:, :, :256]
-        out.append((tiles, 0, full * 256))
-    if V % 256:
-        out.append((narrow[:, full * 256 * per:full * 256 * per + V % 256], full * 256, V))
-    return out
-
-
-def _compact_narrowed(acc: torch.Tensor, dtype, V: int) -> torch.Tensor:
-    """dW (H, V) in ``dtype`` from the accumulator the last chunk narrowed in place; for fp32 the accumulator itself."""
-    if dtype == torch.float32:
-        return acc
-    H = acc.shape[0]
-    dW = _aligned_rows_like((H, V), dtype, acc.device)
-    for tiles, c0, c1 in _narrowed_tiles(acc, dtype, V):
-        dst = dW[:, c0:c1]
-        if tiles.dim() == 3:
-            base = dW if dW.is_contiguous() else dW._base
-            base[:, :c1].view(H, tiles.shape[1], 256).copy_(tiles)
-        else:
-            dst.copy_(tiles)
-    return dW
+    return out5, dx, dW, workspace
 
 
 def _device_guard(t: torch.Tensor):
@@ -735,8 +721,8 @@ class LinearCrossEntropyLoss(torch.nn.Linear):
     ``logit_norm``, ``logit_max``, ``logit_entropy`` and ``z_value``, defined as in the reference's
     ``reference_torch`` (ops.py:9-17).
 
-    Differences from the reference, all of them relaxations: any number of rows, H % 8 and any V (the
-    reference needs N % 512, H % 256, V % 4096), there is no autotuning on the first call, and gradients are
+    Differences from the reference, all of them relaxations: any number of rows, any H and any V (the
+    reference needs N % 512, H % 256, V % 4096; sizes that are not multiples of 8 run on padded copies), there is no autotuning on the first call, and gradients are
     only computed when an input requires them.
     """
 
@@ -755,7 +741,7 @@ class LinearCrossEntropyLoss(torch.nn.Linear):
         factory_kwargs = {"device": device, "dtype": dtype}
         torch.nn.Module.__init__(self)  # not nn.Linear.__init__: no bias, transposed weight
 
-        assert in_features % 8 == 0
+        assert in_features >= 1
         assert out_features >= 1
         assert N_chunk_size >= 1
         assert logit_scale > 0

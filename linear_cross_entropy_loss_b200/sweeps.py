@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import argparse
 import csv
+import os
 import statistics
 from pathlib import Path
 
@@ -32,7 +33,8 @@ RANGES = {  # powers of two, as in the reference (range_dict, bench_fusions.py:1
     "memory": {"H": range(8, 14), "V": range(8, 18), "N": range(8, 17)},
     "accuracy": {"H": range(8, 14), "V": range(8, 18), "N": range(8, 16)},
 }
-PROVIDER = "lce-b200"
+# provider column; a fixed slab mode (LCE_SLAB_MODE=row|tile, see ops.SlabModePolicy) is named in it
+PROVIDER = "lce-b200" + {"row": "-slab-per-row", "tile": "-slab-per-tile"}.get(os.environ.get("LCE_SLAB_MODE", ""), "")
 
 
 def _dtype(acc: str) -> torch.dtype:

@@ -52,6 +52,10 @@ CONFIGS = {
                                   z_regularization=1e-4, labels="zipf", seed=5),
     # small case for profiler captures: operands larger than L2, about 1 GB on the device
     "profile_small_bf16": Config("profile_small_bf16", 4096, 2048, 32768, torch.bfloat16, 4096, seed=6),
+    # the same in fp16 (per-tile slabs: the in-place slab transform runs), and with two chunks (the dW contraction
+    # then runs once writing and once accumulating)
+    "profile_small_fp16": Config("profile_small_fp16", 4096, 2048, 32768, torch.float16, 4096, seed=6),
+    "profile_small_2chunks_bf16": Config("profile_small_2chunks_bf16", 8192, 2048, 32768, torch.bfloat16, 4096, seed=6),
     # the headline metric's point: default shape in bf16, options off
     "headline_bf16": Config("headline_bf16", 16384, 2048, 131072, torch.bfloat16, 4096, seed=1),
 }

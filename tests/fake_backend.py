@@ -104,30 +104,20 @@ class FakeBackend:
         dx[row0:row0 + rows] = table.reduced.pop(epoch)
         del table.scattered[epoch]
 
-    def dw_chunk(self, prob, x, row0, rows, workspace, dW_acc, first, dW_final):
+    def dw_chunk(self, prob, x, row0, rows, workspace, dW, dW_res, first, last):
         self.calls.append("dw_chunk")
         st = self.state[workspace.data_ptr()]
         coef = prob.logit_scale / st["n_valid"]
         keys = sorted(k for k in st["dz"] if row0 <= k < row0 + rows)
         dz = np.concatenate([st["dz"].pop(k) for k in keys])
         assert dz.shape[0] == rows
-        g = torch.from_numpy(x[row0:row0 + rows].double().numpy().T @ dz * coef).float()
-        total = g if first else dW_acc + g
-        if dW_final is not None and dW_acc is not None and dW_final.data_ptr() == dW_acc.data_ptr():
-            # the finished sum overwrites the accumulator, narrowed tile by tile (see lce_dw_chunk)
-            dtype = {0: torch.float16, 1: torch.bfloat16, 2: torch.float32}[prob.dtype]
-            if dtype == torch.float32:
-                dW_acc.copy_(total)
-            else:
-                from linear_cross_entropy_loss_b200 import ops
-
-                for tiles, c0, c1 in ops._narrowed_tiles(dW_acc, dtype, total.shape[1]):
-                    src = total[:, c0:c1].to(dtype)
-                    tiles.copy_(src.view(src.shape[0], -1, 256) if tiles.dim() == 3 else src)
-        elif dW_final is not None:
-            dW_final.copy_(total.to(dW_final.dtype))
-        else:
-            dW_acc.copy_(total)
+        total = torch.from_numpy(x[row0:row0 + rows].double().numpy().T @ dz * coef)
+        if not first:  # the running sum is dW + dW_res (the residual only exists for 16-bit types)
+            total = total + dW.double() + (dW_res.double() if dW_res is not None else 0)
+        dW.copy_(total.to(dW.dtype))
+        if dW_res is not None and not last:
+            dW_res.copy_((total - dW.double()).to(dW.dtype))
+        assert dW_res is not None or dW.dtype == torch.float32 or (first and last)
 
     def finalize(self, prob, workspace, out5):
         self.calls.append("finalize")

@@ -162,14 +162,13 @@ def test_peak_extra_memory_stays_below_one_fp32_chunk_of_logits():
     torch.cuda.synchronize()
     peak = torch.cuda.max_memory_allocated() - before
     budget = cfg.N_chunk_size * cfg.V * 4               # one fp32 chunk of logits: the reference's stated peak
-    # Everything the call allocates, gradients and the fp32 dW accumulator included (the reference's own figure for
-    # bf16 is 3.39 GiB, BASELINE: bench-mem). Alive at the peak: workspace (slab N_chunk x V x 2 bytes, statistics,
-    # split-K partials of dx) + fp32 dW accumulator (H x V x 4) + dx; the bf16 dW is produced inside the accumulator
-    # and compacted after the workspace is gone.
+    # Everything the call allocates, gradients included (the reference's own figure for bf16 is 3.39 GiB, BASELINE:
+    # bench-mem). Alive at the peak: workspace (slab N_chunk x V x 2 bytes, statistics, split-K partials of dx) + dW
+    # and its residual (H x V x 2 bytes each: the sum over the chunks is carried as a pair of bf16 arrays) + dx.
     expected = cfg.N_chunk_size * cfg.V * 2 + cfg.H * cfg.V * 4 + cfg.N * cfg.H * 2
     assert peak <= expected + (224 << 20), (peak, expected)
     assert peak <= 1.13 * budget, (peak, budget)        # 2.24 GiB against the 2 GiB figure, all inclusive
-    excl = peak - cfg.H * cfg.V * 4 - cfg.N * cfg.H * 2  # without what the reference also keeps (fp32 dW, dx)
+    excl = peak - cfg.H * cfg.V * 4 - cfg.N * cfg.H * 2  # without dW + residual and dx (the reference keeps fp32 dW, dx)
     assert excl <= 0.6 * budget, (excl, budget)
 
 

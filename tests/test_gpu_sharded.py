@@ -32,7 +32,8 @@ def test_emulated_shards_on_one_gpu(world):
     ws = [torch.empty(be.workspace_bytes(p), dtype=torch.uint8, device="cuda") for p in probs]
     parts = torch.empty(world, 6 * chunk, dtype=torch.float32, device="cuda")
     dxs = [torch.zeros(N, H, dtype=torch.float32, device="cuda") for _ in range(world)]
-    dWs = [torch.empty(H, vl, dtype=torch.float32, device="cuda") for _ in range(world)]
+    dWs = [torch.empty(H, vl, dtype=dtype, device="cuda") for _ in range(world)]
+    res = [torch.empty(H, vl, dtype=dtype, device="cuda") for _ in range(world)]
     outs = [torch.empty(5, dtype=torch.float32, device="cuda") for _ in range(world)]
     for g in range(world):
         be.begin(probs[g], yd, ws[g])
@@ -43,7 +44,7 @@ def test_emulated_shards_on_one_gpu(world):
             be.combine_chunk(probs[g], parts, yd, row0, chunk, ws[g])
             be.dz_chunk(probs[g], xd, yd, row0, chunk, ws[g])
             be.dx_chunk(probs[g], slabs[g], row0, chunk, ws[g], dxs[g])
-            be.dw_chunk(probs[g], xd, row0, chunk, ws[g], dWs[g], row0 == 0, None)
+            be.dw_chunk(probs[g], xd, row0, chunk, ws[g], dWs[g], res[g], row0 == 0, row0 + chunk >= N)
     for g in range(world):
         be.finalize(probs[g], ws[g], outs[g])
     torch.cuda.synchronize()
@@ -163,7 +164,8 @@ def test_emulated_pipelined_pass_with_the_row_partials_exchange(world, dtype, N,
     ref = oracle.forward_backward(x, y, W, -1, 1e-3, 0.5)
     for n_pass in range(2):
         dxs = [torch.zeros(N, H, dtype=torch.float32, device="cuda") for _ in range(world)]
-        dWs = [torch.empty(H, vl, dtype=torch.float32, device="cuda") for _ in range(world)]
+        dWs = [torch.empty(H, vl, dtype=dtype, device="cuda") for _ in range(world)]
+        res = [None if dtype == torch.float32 else torch.empty(H, vl, dtype=dtype, device="cuda") for _ in range(world)]
         outs = [torch.empty(5, dtype=torch.float32, device="cuda") for _ in range(world)]
         for g in range(world):
             be.begin(probs[g], yd, ws[g])
@@ -185,7 +187,7 @@ def test_emulated_pipelined_pass_with_the_row_partials_exchange(world, dtype, N,
                 be.combine_chunk_peer(probs[g], tables[g], epochs[ci], yd, r0, n, ws[g], 2000)
                 be.dz_chunk(probs[g], xd, yd, r0, n, ws[g])
                 be.dx_chunk(probs[g], slabs[g], r0, n, ws[g], dxs[g])
-                be.dw_chunk(probs[g], xd, r0, n, ws[g], dWs[g], ci == 0, None)
+                be.dw_chunk(probs[g], xd, r0, n, ws[g], dWs[g], res[g], ci == 0, ci == len(chunks) - 1)
         for g in range(world):
             be.finalize(probs[g], ws[g], outs[g])
         torch.cuda.synchronize()
