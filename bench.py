@@ -34,12 +34,12 @@ METRIC = "fwd+bwd TFLOP/s (6NHV/t)"
 PUBLISHED_BF16_DEFAULT_TFLOPS = 86.75
 # fallback roofline denominators when the measured-peaks file is absent (earlier measurement on this pool)
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of each contraction kernel, from an ncu
-# capture of the quarter-size case (N=4096, H=2048, V=32768, bf16; summary kept under profiles/). Forward and dx
-# traffic grow in proportion to V; the figures are scaled by V_local / 32768 at run time (only for N_chunk_size=4096,
-# H=2048, which the capture used). dW is not scaled: from the second chunk on it also reads and rewrites the fp32
-# accumulator, which the one-chunk capture does not contain.
-NCU_DRAM_BYTES_V32768 = {"fwd": 391.4e6, "dx": 738.5e6, "dw": None}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of each contraction kernel, from ncu
+# captures of the quarter-size case (N=4096, H=2048, V=32768, bf16; summary kept under profiles/). All three grow in
+# proportion to V; the figures are scaled by V_local / 32768 at run time (only for N_chunk_size=4096, H=2048, which
+# the captures used). dW: average over the four launches of a four-chunk pass (the first writes the sum and residual
+# arrays, the middle ones read and write both, the last reads both and writes the sum), from the two-chunk capture.
+NCU_DRAM_BYTES_V32768 = {"fwd": 388.3e6, "dx": 735.7e6, "dw": 728.6e6}
 
 
 def parse_args():
