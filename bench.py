@@ -326,6 +326,8 @@ def run_reference_arm(args, cfg, n_gpus):
         "scaling": args.scaling if n_gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": config_dict(cfg, n_gpus, args),
         "cpu_baseline": info,
+        "ms_per_step_note": "a step of this arm is one bounded row sample (cpu_baseline.sample), not the whole "
+                            "workload: only the rate compares with the GPU arm, and it scales with cpu_baseline.cores",
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }

@@ -434,7 +434,8 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     if peer is not None and getattr(peer, "overlap", False):
         xstream = _side_stream(dev, "exchange")
 
-    if shard is None and not use_side and hasattr(backend, "fused_pass"):
+    if (shard is None and not use_side and hasattr(backend, "fused_pass")
+            and os.environ.get("LCE_FUSED_PASS", "1") != "0"):
         # unsharded, one stream: the whole pass is ONE call into the library (same kernels, same order as the loop
         # below; what it saves is host time per call, which is all that small problems cost)
         backend.fused_pass(prob, x, At, y, workspace, row_parts, dx, dW, dW_res, out5)

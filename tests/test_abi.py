@@ -130,6 +130,29 @@ def test_null_pointers_are_rejected(lib):
     assert lib.lce_workspace_bytes(None, None) == -1
 
 
+def test_one_call_pass_checks_its_arguments_before_touching_a_device(lib):
+    p = problem()
+    args = lambda prob, **kw: (ctypes.byref(prob), 16, 256, 16, 4096, 16, kw.get("ws", 16), 16, kw.get("dx", 16), 256, 1,
+                               kw.get("dw", 16), 4096, 16, 4096, 16, None)
+    assert lib.lce_fused_pass(*args(problem(world=2))) == -1          # sharded callers issue the steps themselves
+    assert lib.lce_fused_pass(*args(p, ws=None)) == -1
+    assert lib.lce_fused_pass(*args(p, dx=None, dw=None)) == -1       # gradients wanted but no output given
+    assert lib.lce_fused_pass(*args(problem(want_grad=0))) == -1      # outputs given but no gradient wanted
+    assert lib.lce_fused_pass(*args(problem(hidden=100))) == -2
+
+
+def test_exchange_buffer_sizes_need_no_device(lib):
+    out = ctypes.c_size_t(0)
+    p = problem(world=4)
+    assert lib.lce_parts_bytes(ctypes.byref(p), ctypes.byref(out)) == 0
+    assert out.value >= 1024 + 4 * 4 * 6 * 256 * 4                      # flags + 4 slots x world x 6 x chunk rows floats
+    assert lib.lce_parts_bytes(ctypes.byref(problem(world=9)), ctypes.byref(out)) == -1
+    two = ctypes.c_size_t(0)
+    assert lib.lce_workspace_bytes(ctypes.byref(problem(chunk_buffers=2)), ctypes.byref(two)) == 0
+    rc, one = workspace_bytes(lib, problem())
+    assert one < two.value < 2 * one
+
+
 def test_chunk_bounds_are_checked(lib):
     p = problem()
     args = (16, 256, 16, 4096, 16)

@@ -390,6 +390,18 @@ def test_randomised_shapes_options_and_modes(seed, monkeypatch):
                          monitoring=bool(seed % 2), loss_tol=loss_tol)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_one_call_pass_equals_the_step_by_step_pass_bit_for_bit(monkeypatch, dtype):
+    """Unsharded passes are issued as ONE library call (lce_fused_pass); LCE_FUSED_PASS=0 issues the same steps one
+    by one from Python. Same kernels in the same order: the results must be identical bit for bit."""
+    x, y, W = random_problem(640, 256, 2048, dtype, seed=21)
+    monkeypatch.setenv("LCE_FUSED_PASS", "1")
+    one = run_gpu(x, y, W, -1, 1e-4, 0.5, 256, True)
+    monkeypatch.setenv("LCE_FUSED_PASS", "0")
+    steps = run_gpu(x, y, W, -1, 1e-4, 0.5, 256, True)
+    assert one[0] == steps[0] and torch.equal(one[1], steps[1]) and torch.equal(one[2], steps[2])
+
+
 def test_device_status_is_clean_after_a_pass():
     from linear_cross_entropy_loss_b200 import ops
     x, y, W = random_problem(256, 256, 512, torch.bfloat16, seed=15)
