@@ -15,6 +15,7 @@ package imports it. When the folder is absent those legs report that the referen
 """
 from __future__ import annotations
 
+import os
 import shutil
 import subprocess
 import sys
@@ -23,7 +24,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 TARGET = HERE / "_ref"
-DEFAULT_CHECKOUT = Path("/root/reference")
+# where the reference checkout is looked for: LCE_REFERENCE_CHECKOUT, else a folder "reference" beside this repository
+DEFAULT_CHECKOUT = Path(os.environ.get("LCE_REFERENCE_CHECKOUT", HERE.parent.parent / "reference"))
 
 
 def installed() -> bool:
