@@ -17,6 +17,7 @@ the oracle's port of it on a bounded sample of the same workload; rank 0 only.
 """
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -346,7 +347,7 @@ def config_dict(cfg, n_gpus, args):
                         else "NCCL all-reduce per chunk, in stream order" if os.environ.get("LCE_DX_REDUCE") == "chunk"
                         else "one NCCL all-reduce of dx per pass"),
         "row_partials_exchange": ("none" if n_gpus == 1 else
-                                  "NCCL all-gather per chunk" if (os.environ.get("LCE_PEER_PARTS") == "0"
+                                  "NCCL all-gather per chunk" if (os.environ.get("LCE_PEER_PARTS", "0") != "1"
                                                                   or os.environ.get("LCE_PEER_DX") == "1")
                                   else "stores into peer memory + flags, chunks software-pipelined on two slabs"),
         "l2": "inputs larger than L2 (the weight alone is >= 512 MiB per GPU); no explicit flush",
@@ -431,8 +432,20 @@ def main():
     if rank == 0:
         sampler.start()   # started before the warm-up so that it is polling by the time the timed region begins
     for _ in range(max(3, args.warmup)):
-        fwd_bwd(x, y)
+        warm_loss = fwd_bwd(x, y)
     barrier()
+    # a pass that is not finite after the warm-up (for instance an exchange between ranks that timed out: the library
+    # then returns NaN) is not worth timing: every rank learns of it and the run ends with an error instead
+    bad = torch.tensor([0.0 if math.isfinite(warm_loss.item()) else 1.0], device=dev)
+    if sharded:
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+    if bad.item() != 0:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "error": "the loss of a warm-up step is not finite", "n_gpus": world}),
+                  flush=True)
+        if sharded:
+            dist.destroy_process_group()
+        sys.exit(4)
     torch.cuda.reset_peak_memory_stats()
     mem_before = torch.cuda.memory_allocated()
     _native.profile_read()

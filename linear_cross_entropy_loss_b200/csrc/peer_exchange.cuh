@@ -91,9 +91,11 @@ __global__ void peer_signal_kernel(PeerBases peers, int world, int rank, int pha
 __device__ __forceinline__ bool peer_wait_all(const uint32_t* flags, int world, uint32_t epoch, long long limit_ns,
                                               int* status) {
   __shared__ int s_fail;
-  if (threadIdx.x == 0) s_fail = 0;
+  // A pass whose status word is already set (an earlier wait of this pass ran out) does not wait again: its loss is
+  // NaN whatever follows, and one expired wait per pass bounds the time a broken exchange can cost.
+  if (threadIdx.x == 0) s_fail = (*reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
   __syncthreads();
-  if (threadIdx.x < world) {
+  if (s_fail == 0 && threadIdx.x < world) {
     const unsigned long long t0 = wall_ns();
     while (int32_t(ld_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
       if ((long long)(wall_ns() - t0) > limit_ns) {

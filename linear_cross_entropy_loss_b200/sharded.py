@@ -8,10 +8,12 @@ and ``y`` are replicated. Per row chunk:
 2. ONE small all-gather (``6 * chunk_rows`` floats per rank) makes all partials visible everywhere and a
    local kernel merges them in rank order into the global log-sum-exp -- bitwise identical on every
    rank, which a max/sum all-reduce pair would not guarantee;
-   By default the partials do not even go through a collective: every rank stores them into all ranks'
+   ``LCE_PEER_PARTS=1`` selects a form without that collective: every rank stores its partials into all ranks'
    peer-mapped buffers and publishes a flag (``PartsExchange``), and the chunks are software-pipelined -- the
    forward of chunk c + 1 is enqueued before the combine and backward of chunk c, on two alternating slabs -- so
-   the partials of a chunk have a whole backward step to arrive before anyone waits for them (bounded waits);
+   the partials of a chunk have a whole backward step to arrive before anyone waits for them (bounded waits).
+   Measured on 2 and 4 x B200 it does not beat the all-gather (22.6-22.8 against 22.3 ms per step on 4 GPUs at the
+   default shape, 45.9 against 45.2 ms on the 65536 x 4096 x 131072 case), so the all-gather stays the default;
 3. every rank forms dZ for its slab, its own dW slab (no communication) and a partial dx, which is
    summed over the ranks with ONE all-reduce of the whole dx at the end of the pass (``LCE_DX_REDUCE=chunk``:
    one all-reduce per chunk, of that chunk's rows, in stream order). ``LCE_PEER_DX=1`` selects the device-side exchange instead (``PeerExchange``): the epilogue of
@@ -141,7 +143,8 @@ class PartsExchange:
 
     Built collectively on first use for a given size and kept for the life of the process. ``next_epoch`` must
     advance identically on all ranks, which it does when all ranks run the same sequence of passes.
-    ``LCE_PEER_PARTS=0`` keeps the all-gather."""
+    Opt-in (``LCE_PEER_PARTS=1``): measured on 2 and 4 x B200 it ties with or loses 1-2 % to the all-gather, and it
+    holds a second slab per rank."""
 
     _cache = {}
     _unavailable = set()
@@ -175,7 +178,7 @@ class PartsExchange:
         values that are equal on all ranks."""
         backend = ops.get_backend()
         world = dist.get_world_size(group)
-        if (os.environ.get("LCE_PEER_PARTS", "1") == "0" or os.environ.get("LCE_PEER_DX", "0") == "1"
+        if (os.environ.get("LCE_PEER_PARTS", "0") != "1" or os.environ.get("LCE_PEER_DX", "0") == "1"
                 or not getattr(backend, "requires_cuda", True) or device.type != "cuda" or world < 2
                 or world > _native.MAX_PEERS):
             return None

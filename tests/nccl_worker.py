@@ -28,10 +28,11 @@ def main():
     for dtype, chunk, cos_min in ((torch.bfloat16, 256, 0.99999), (torch.float16, 1024, 0.999995)):
         x, y, W = random_problem(N, H, V, dtype, seed=0)
         ref = oracle.forward_backward(x, y, W, -1, 1e-4, 0.5)
-        # three data paths: dx summed by the contraction's own stores into peer-mapped memory; the default (row
-        # partials pushed over peer memory, chunks pipelined, ONE all-reduce of dx per pass); the plain collectives
-        # (all-gather of the partials and an all-reduce of dx per chunk)
-        for peer_dx, peer_parts, dx_reduce in (("1", "1", "pass"), ("0", "1", "pass"), ("0", "0", "chunk")):
+        # four data paths: dx summed by the contraction's own stores into peer-mapped memory; row partials pushed
+        # over peer memory with pipelined chunks and ONE all-reduce of dx per pass; the default (all-gather of the
+        # partials per chunk, one all-reduce of dx per pass); all-gather and all-reduce per chunk
+        for peer_dx, peer_parts, dx_reduce in (("1", "0", "pass"), ("0", "1", "pass"), ("0", "0", "pass"),
+                                               ("0", "0", "chunk")):
             os.environ["LCE_PEER_DX"] = peer_dx
             os.environ["LCE_PEER_PARTS"] = peer_parts
             os.environ["LCE_DX_REDUCE"] = dx_reduce

@@ -223,6 +223,12 @@ def test_wait_for_row_partials_runs_out_and_reports():
     torch.cuda.synchronize()
     assert 150 < t0.elapsed_time(t1) < 2000
     assert be.read_status(ws) == -6  # LCE_ERR_DEVICE_TIMEOUT
+    # a pass whose status word is set does not wait again: a broken exchange costs one expired wait per pass
+    t0.record()
+    be.combine_chunk_peer(prob, _tables(bufs)[0], 2, y, 0, N, ws, 200)
+    t1.record()
+    torch.cuda.synchronize()
+    assert t0.elapsed_time(t1) < 50
     out5 = torch.zeros(5, dtype=torch.float32, device="cuda")
     be.finalize(prob, ws, out5)
     assert torch.isnan(out5[0])
