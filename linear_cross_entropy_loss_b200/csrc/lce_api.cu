@@ -125,23 +125,30 @@ int validate_problem(const lce_problem* p) {
   return LCE_OK;
 }
 
-// K-split of the dx contraction (K = vocab_local): the smallest split whose work units fill the
-// SMs to >= 95 % in whole waves; the partials are reduced in a fixed order afterwards.
+// K-split of the dx contraction (K = vocab_local). More splits fill the SMs in whole waves (128 tiles on 74 CTA pairs
+// are 1.73 waves; four times as many units are 6.92) but cost fp32 partials that a second kernel has to sum; one
+// split lets the contraction write dx itself. The choice minimises a small cost model: contraction time at the wave
+// efficiency of the split + time of the partial traffic (rates measured on B200: 1.3 PFLOP/s, 4.5 TB/s).
 int choose_dx_splits(const lce_problem* p, int sms) {
   const long long tiles = (p->chunk_rows / BLOCK_M) * (hidden_pad(p) / BLOCK_N);
   const long long kblocks = vocab_pad(p) * elem_size(p->dtype) / 128;
+  const double gemm_us = 2.0 * (double)p->chunk_rows * (double)hidden_pad(p) * (double)vocab_pad(p) / 1.3e9;
+  const double row_elems = (double)p->chunk_rows * (double)hidden_pad(p);
   int best = 1;
-  double best_eff = 0.0;
+  double best_us = 0.0;
   for (int s = 1; s <= 16; s *= 2) {
-    if (kblocks % s != 0 || kblocks / s < 8) break;
+    if (kblocks % s != 0 || (s > 1 && kblocks / s < 8)) break;
     const long long units = tiles * s;
     const long long waves = (units + sms - 1) / sms;
     const double eff = (double)units / (double)(waves * sms);
-    if (eff > best_eff + 1e-9) {
-      best_eff = eff;
+    // the reduction reads s fp32 partials and writes the result once, plus a launch and its gap; the partial
+    // stores overlap the contraction and are charged at half their traffic (they cost energy more than time)
+    const double extra_us = s == 1 ? 0.0 : row_elems * (6.0 * s + 2.0) / 4.5e6 + 4.0;
+    const double us = gemm_us / eff + extra_us;
+    if (s == 1 || us < best_us) {
+      best_us = us;
       best = s;
     }
-    if (eff >= 0.95) return s;
   }
   return best;
 }
@@ -723,8 +730,11 @@ PeerBases bases_of(const lce_peer_table* peers) {
 
 // partials[s] = dZ * W^T over K-split s of the vocabulary, scaled by logit_scale / n_valid: into the workspace
 // (scatter == nullptr) or into the owners' receive buffers.
+// direct_dx (optional, one split only): the rows of dx themselves, element type of x, row stride direct_ld; the
+// epilogue then writes them instead of fp32 partials.
 int launch_dx_gemm(const lce_problem* p, const void* weight, int64_t w_ld, int64_t row0, int64_t rows,
-                   const Workspace& w, int sms, cudaStream_t st, const PeerScatter* scatter) {
+                   const Workspace& w, int sms, cudaStream_t st, const PeerScatter* scatter, void* direct_dx = nullptr,
+                   int64_t direct_ld = 0) {
   const int es = elem_size(p->dtype);
   const long long local0 = row0 % p->chunk_rows;
   const long long v_pad = vocab_pad(p), h_pad = hidden_pad(p);
@@ -758,7 +768,17 @@ int launch_dx_gemm(const lce_problem* p, const void* weight, int64_t w_ld, int64
   gp.row_coef = row_reference_mode(p) ? w.row_coef + local0 : nullptr;
   gp.status = &w.scalars->status;
   CUtensorMap tc = ta;
-  if (scatter == nullptr && epilogue_tma_enabled()) {
+  if (direct_dx != nullptr) {
+    // plain conversion and store of coef * row_coef * acc; rows and columns beyond dx are masked
+    char* rows0 = reinterpret_cast<char*>(direct_dx) + (size_t)row0 * (size_t)direct_ld * es;
+    gp.out_sum = rows0;
+    gp.out_res = nullptr;
+    gp.out_pair_ld = direct_ld;
+    gp.out_pair_last = 1;
+    gp.out_rows = (int)rows;
+    gp.out_cols = (int)p->hidden;
+    gp.out_vector_ok = ((reinterpret_cast<uintptr_t>(rows0) & 31u) == 0 && ((direct_ld * es) & 31) == 0) ? 1 : 0;
+  } else if (scatter == nullptr && epilogue_tma_enabled()) {
     // the partials [splits][chunk_rows][h_pad] seen as one fp32 matrix of splits * chunk_rows rows
     if ((v = make_store_tmap(&tc, LCE_DTYPE_F32, w.dx_part, h_pad, (long long)w.dx_splits * p->chunk_rows, h_pad)) !=
         LCE_OK)
@@ -799,6 +819,10 @@ int lce_dx_chunk(const lce_problem* p, const void* weight, int64_t w_ld, int64_t
   const Workspace w = layout_workspace(p, workspace, sms, chunk_buffer_of(p, row0));
   const long long local0 = row0 % p->chunk_rows;
   const long long h_pad = hidden_pad(p);
+  if (w.dx_splits == 1 && dx_dtype == p->dtype) {
+    // one split: the contraction's epilogue scales, converts and stores the dx rows itself
+    return launch_dx_gemm(p, weight, w_ld, row0, rows, w, sms, st, nullptr, dx, dx_ld);
+  }
   if ((v = launch_dx_gemm(p, weight, w_ld, row0, rows, w, sms, st, nullptr)) != LCE_OK) return v;
 
   // fixed-order sum of the partials -> dx rows
