@@ -375,7 +375,8 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
         A_pad[H:] = 0
         out5, dx, dW, workspace = run_pass(x_pad, y, A_pad, ignore_index, z_regularization, logit_scale, N_chunk_size,
                                            monitoring, (want_dx, want_dW), shard)
-        return out5, (None if dx is None else dx[:, :H].contiguous()), (None if dW is None else dW[:H]), workspace
+        # dx stays a view of the padded buffer: its rows keep the 16-byte alignment the rescaling kernel of backward needs
+        return out5, (None if dx is None else dx[:, :H]), (None if dW is None else dW[:H]), workspace
     # rows per chunk as in the reference (ops.py:687), rounded up to the 128-row tile of the kernels
     N_group = -(-min(N, int(N_chunk_size)) // 128) * 128
 
@@ -629,7 +630,7 @@ def fused_pass_op(x: torch.Tensor, y: torch.Tensor, At: torch.Tensor, ignore_ind
                                    monitoring, want_grad)
     if not want_grad:
         return out5, x.new_empty(0), At.new_empty(0)
-    return out5, dx.view(x.shape), dA
+    return out5, dx.reshape(x.shape), dA
 
 
 @fused_pass_op.register_fake
