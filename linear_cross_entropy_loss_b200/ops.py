@@ -240,6 +240,7 @@ class ShardSpec:
 # A chunk whose row count allows it is processed as this many sub-chunks, so that the memory-bound slab transform
 # of one sub-chunk runs on a second stream underneath the tensor-core kernels of the other.
 SUBCHUNKS = 2
+MIN_SPLIT_ELEMS = 1 << 25  # slab elements of a chunk from which halving pays (equal on all ranks of a sharded run)
 _side_streams: dict = {}
 
 
@@ -384,7 +385,10 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     policy_key = (x.device.index, x.dtype, H, V, N_group, world)
     slab_mode = slab_mode_policy.choose(policy_key, x.dtype)
     per_tile = slab_mode == _native.SLAB_PER_TILE
-    split = _wants_subchunks(per_tile, want_grad, x.dtype, shard is not None)
+    # chunks too small to halve, or whose slab pass is too short to be worth hiding (the per-step calls from Python
+    # then cost more than the overlap gains), run whole on one stream -- unsharded as one library call
+    split = (_wants_subchunks(per_tile, want_grad, x.dtype, shard is not None)
+             and len(_split_rows(0, N_group, True)) > 1 and N_group * V >= MIN_SPLIT_ELEMS)
     prob = Problem(
         n_rows_total=N, chunk_rows=N_group, hidden=H, vocab_local=V,
         vocab_offset=0 if shard is None else shard.vocab_offset, ignore_index=int(ignore_index), world=world,
@@ -414,8 +418,7 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
             dW_res = _aligned_rows_like((H, V), At.dtype, dev)
 
     # second stream only where sub-chunks exist (per-tile slabs); everything else runs in order on the caller's stream
-    use_side = (native and dev.type == "cuda" and split and SUBCHUNKS == 2
-                and len(_split_rows(0, N_group, True)) > 1)  # chunks too small to halve run on one stream
+    use_side = native and dev.type == "cuda" and split and SUBCHUNKS == 2
     main = torch.cuda.current_stream(dev) if use_side else None
     side = _side_stream(dev) if use_side else None
 
