@@ -64,7 +64,11 @@ def _worker(rank, world, port, results):
 
 @pytest.mark.parametrize("world", [2, 4])
 def test_vocab_sharded_pass_over_gloo(world):
-    port = 29400 + world + (os.getpid() % 500)
+    import socket
+
+    with socket.socket() as sock:  # a port that is free right now (a fixed one can still be in TIME_WAIT from an earlier run)
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     with mp.Manager() as manager:
         results = manager.dict()
         mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
