@@ -276,7 +276,8 @@ class SlabModePolicy:
     The default mode keeps one base per row and recomputes the row groups whose logits leave the window around
     it; with very wide logits (standard deviation of a row's logits beyond about 50, e.g. the reference's
     ``A~randn`` benchmark inputs at H >= 4096) that happens in most chunks and the per-tile mode is faster.
-    ``LCE_SLAB_MODE=row|tile`` fixes the mode; ``auto`` (default) starts in the default mode, reads -- without
+    ``LCE_SLAB_MODE=row|tile`` fixes the mode; ``auto`` (default) uses per-tile slabs for small chunks (below 2^24
+    slab elements, where launches count and the slab pass does not) and otherwise starts in the default mode, reads -- without
     ever synchronising: a pinned-memory copy plus an event that is only polled -- how many row groups the last
     finished pass of the same shape recomputed, switches to per-tile above ``threshold`` and tries the default
     mode again every ``retry_every`` passes. Polling an event is not allowed while a stream is being captured
@@ -285,6 +286,9 @@ class SlabModePolicy:
 
     threshold = 0.25
     retry_every = 64
+    # chunks whose slab has fewer elements than this always use per-tile slabs: the in-place pass over such a slab
+    # takes microseconds, and the mode needs fewer launches per chunk (no conditional re-run pair, no probe)
+    small_slab_elems = 1 << 24
 
     def __init__(self):
         self.history = {}
@@ -296,6 +300,8 @@ class SlabModePolicy:
         if forced == "row":
             return _native.SLAB_DEFAULT
         if forced == "tile":
+            return _native.SLAB_PER_TILE
+        if key[3] * key[4] < self.small_slab_elems:  # key = (device, dtype, H, V, rows per chunk, world)
             return _native.SLAB_PER_TILE
         h = self.history.get(key)
         if h is None:

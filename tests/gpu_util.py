@@ -48,6 +48,21 @@ def run_gpu(x, y, W, ignore=-100, zreg=0.0, scale=1.0, chunk=4096, monitoring=Tr
 
 def check_against_oracle(x, y, W, dtype, ignore=-100, zreg=0.0, scale=1.0, chunk=4096, monitoring=True,
                          loss_tol=None):
+    """The pass as a user gets it (slab mode chosen by the library) against the float64 oracle; for bf16 / fp32 also
+    with one base per row forced, the mode of large problems, which the library does not pick for small chunks."""
+    import os
+
+    result = _check_against_oracle(x, y, W, dtype, ignore, zreg, scale, chunk, monitoring, loss_tol)
+    if dtype != torch.float16 and "LCE_SLAB_MODE" not in os.environ:
+        os.environ["LCE_SLAB_MODE"] = "row"
+        try:
+            _check_against_oracle(x, y, W, dtype, ignore, zreg, scale, chunk, monitoring, loss_tol)
+        finally:
+            del os.environ["LCE_SLAB_MODE"]
+    return result
+
+
+def _check_against_oracle(x, y, W, dtype, ignore, zreg, scale, chunk, monitoring, loss_tol):
     got, dx, dW = run_gpu(x, y, W, ignore, zreg, scale, chunk, monitoring)
     ref = oracle.forward_backward(x, y, W, ignore, zreg, scale)
     tol = dict(TOL[dtype])

@@ -348,6 +348,7 @@ def test_slab_mode_policy_switches_after_passes_that_recompute(monkeypatch):
     from linear_cross_entropy_loss_b200 import _native, ops
 
     monkeypatch.delenv("LCE_SLAB_MODE", raising=False)
+    monkeypatch.setattr(ops.SlabModePolicy, "small_slab_elems", 0)  # small chunks would always use per-tile slabs
     policy = ops.slab_mode_policy
     policy.history.clear()
     x, y, W = random_problem(1024, 256, 4096, torch.bfloat16, seed=34)

@@ -361,6 +361,8 @@ def test_slab_mode_policy_decisions(monkeypatch):
     key = (0, torch.bfloat16, 2048, 131072, 4096, 1)
     assert pol.choose(key, torch.float16) == _native.SLAB_PER_TILE
     assert pol.choose(key, torch.bfloat16) == _native.SLAB_DEFAULT            # nothing known yet
+    small = (0, torch.bfloat16, 256, 4096, 256, 1)                              # a chunk of 2^20 slab elements
+    assert pol.choose(small, torch.bfloat16) == pol.choose(small, torch.float32) == _native.SLAB_PER_TILE
     pol.history[key] = {"host": torch.tensor([12, 16], dtype=torch.int32), "event": PendingEvent(), "fraction": 0.0,
                         "tile_passes": 0}
     assert pol.choose(key, torch.bfloat16) == _native.SLAB_DEFAULT            # counters not there yet: no waiting
