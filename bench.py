@@ -455,17 +455,31 @@ def main():
     barrier()
     sampler.mark_start()
     e0.record()
+    marks = []
     for i in range(args.steps):
         loss = fwd_bwd(x, y, keep_grads=(i == args.steps - 1))  # the last timed step's gradients are checked below
+        marks.append(torch.cuda.Event(enable_timing=True))
+        marks[-1].record()                                       # per-step durations for the quantiles (no sync)
     e1.record()
     barrier()
     sampler.mark_end()
     launches = _native.launch_count() - launches_before
     _native.profile_enable(False)
     kernel_ms, kernel_launches = _native.profile_read()
+    # every rank's own time inside the three contractions per step: with a sharded run the step is set by the slowest
+    # rank (each GPU settles at its own clock under its power cap), and this shows how far apart the ranks are
+    mine = torch.tensor([sum(kernel_ms.values()) / args.steps], dtype=torch.float64, device=dev)
+    if sharded:
+        all_ranks = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(all_ranks, mine)
+        rank_contraction_ms = [round(t.item(), 3) for t in all_ranks]
+    else:
+        rank_contraction_ms = [round(mine.item(), 3)]
     clocks = sampler.stop() if rank == 0 else None
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_per_step = ms_total / args.steps
+    per_step = sorted(a.elapsed_time(b) for a, b in zip([e0] + marks[:-1], marks))  # this rank's steps
+    quantiles = [per_step[min(len(per_step) - 1, int(q * len(per_step)))] for q in (0.2, 0.5, 0.8)]
     peak_extra = torch.cuda.max_memory_allocated() - mem_before
     value = cfg.flops / (ms_per_step * 1e-3) / 1e12
     loss_value = loss.item()
@@ -548,7 +562,11 @@ def main():
 
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
+        "ms_per_step_quantiles": {"p20": quantiles[0], "p50": quantiles[1], "p80": quantiles[2],
+                                  "note": "rank 0's individual steps (the reference's benchmark reports median and "
+                                          "20 / 80 % quantiles, bench_fusions.py:271,280)"},
+        "higher_is_better": True,
         "scaling": args.scaling if world > 1 else "weak",
         "vs_baseline": value / PUBLISHED_BF16_DEFAULT_TFLOPS if (world == 1 and cfg.name == "headline_bf16") else None,
         "dtype": str(cfg.dtype).split(".")[-1].replace("bfloat16", "bf16").replace("float16", "f16").replace("float32", "tf32"),
@@ -557,6 +575,7 @@ def main():
                 "h2d_bytes_per_step": x_host.numel() * x_host.element_size() + y_host.numel() * 8,
                 "d2h_bytes_per_step": 4},
         "gpu_launches": launches, "roofline": roofline, "loss": loss_value, "parity": parity,
+        "contraction_ms_per_step_by_rank": rank_contraction_ms,
         "peak_extra_bytes": peak_extra, "peak_budget_bytes": min(cfg.N, cfg.N_chunk_size) * v_local * 4,
         # the same without the gradients the caller receives and the residual array of dW (together what the
         # reference's fp32 gradient buffers hold)
