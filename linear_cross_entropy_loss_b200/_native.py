@@ -170,7 +170,7 @@ SIGNATURES = {
     "lce_profile_read": (ctypes.c_int, [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]),
     "lce_debug_gemm": (
         ctypes.c_int,
-        [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _vp],
+        [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp, _vp],
     ),
 }
 

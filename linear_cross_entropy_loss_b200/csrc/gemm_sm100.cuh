@@ -71,6 +71,9 @@ struct GemmParams {
   int splits;
   int k_blocks;  // K-blocks (128 bytes of K each) per split
   int n_fastest; // 0: consecutive units walk M first (then N, then the K-split); 1: they walk N first
+  int raster_group;  // kernels: 0 = walk the whole fast dimension, G > 0 = in bands of G tiles (unit_to_tile).
+                     // Given to launch_gemm: 0 = the process default (no bands unless LCE_RASTER_GROUP asks),
+                     // -1 = no bands, -2 = chosen from the shape, G > 0 = bands of G
   // element offsets added to the tensor-map coordinates
   int a_mn0, a_k0, b_mn0, b_k0;
 
@@ -686,6 +689,33 @@ __device__ __forceinline__ bool tile_selected(const GemmParams& p, int row0, int
   return any != 0;
 }
 
+// Tile of the `rem`-th unit of one K-split. Without bands (raster_group == 0) the fast dimension -- M, or N when
+// n_fastest -- is walked completely before the slow one advances, so the units in flight at one time cover the
+// whole fast dimension times a few slow tiles. With raster_group = G the fast dimension is cut into bands of G
+// tiles and each band is walked over the whole slow dimension before the next band starts: the units in flight
+// form a block of about G x (CTAs / G) tiles. When the fast dimension is long this block shares more operand rows
+// per byte fetched, and the band's operand (G tiles x K) can stay in L2 while the other operand streams past it,
+// instead of being fetched from DRAM again for every slow tile.
+__device__ __forceinline__ void unit_to_tile(const GemmParams& p, int rem, int& m_blk, int& n_blk) {
+  const int nf = p.n_fastest ? p.n_tiles : p.m_tiles;
+  int f, s;
+  if (p.raster_group <= 0 || p.raster_group >= nf) {
+    s = rem / nf;
+    f = rem - s * nf;
+  } else {
+    const int ns = p.n_fastest ? p.m_tiles : p.n_tiles;
+    const int per_band = p.raster_group * ns;  // the last band may be narrower; it is the only one
+    const int band = rem / per_band;
+    const int r = rem - band * per_band;
+    const int f0 = band * p.raster_group;
+    const int width = min(p.raster_group, nf - f0);
+    s = r / width;
+    f = f0 + (r - s * width);
+  }
+  m_blk = p.n_fastest ? s : f;
+  n_blk = p.n_fastest ? f : s;
+}
+
 // --------------------------------------------------------------------------------------------------
 // the kernel
 // --------------------------------------------------------------------------------------------------
@@ -756,8 +786,8 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
         const int split = unit / tiles_mn;
         const int rem = unit - split * tiles_mn;
-        const int n_blk = p.n_fastest ? rem % p.n_tiles : rem / p.m_tiles;
-        const int m_blk = p.n_fastest ? rem / p.n_tiles : rem - n_blk * p.m_tiles;
+        int m_blk, n_blk;
+        unit_to_tile(p, rem, m_blk, n_blk);
         const int a_mn = p.a_mn0 + m_blk * BLOCK_M;
         const int b_mn = p.b_mn0 + n_blk * BLOCK_N;
         if (!tile_selected(p, m_blk * BLOCK_M, BLOCK_M)) continue;
@@ -803,7 +833,8 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       for (int unit = blockIdx.x; ok && unit < units; unit += gridDim.x) {
         if (p.run_mask != nullptr) {  // same tile selection as the producer and the epilogue warps
           const int rem = unit % tiles_mn;
-          const int m_sel = p.n_fastest ? rem / p.n_tiles : rem % p.m_tiles;
+          int m_sel, n_sel;
+          unit_to_tile(p, rem, m_sel, n_sel);
           if (!tile_selected(p, m_sel * BLOCK_M, BLOCK_M)) continue;
         }
         if (!mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
@@ -854,8 +885,8 @@ lce_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
       const int split = unit / tiles_mn;
       const int rem = unit - split * tiles_mn;
-      const int n_blk = p.n_fastest ? rem % p.n_tiles : rem / p.m_tiles;
-      const int m_blk = p.n_fastest ? rem / p.n_tiles : rem - n_blk * p.m_tiles;
+      int m_blk, n_blk;
+      unit_to_tile(p, rem, m_blk, n_blk);
       if (!tile_selected(p, m_blk * BLOCK_M, BLOCK_M)) continue;
       if (!mbar_wait_warp(&sh->acc_full[acc], acc_phase, abort_flag)) {
         if (lane == 0) atomicCAS(p.status, DEV_OK, DEV_WAIT_TIMEOUT_EPILOGUE);
@@ -1007,8 +1038,8 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       for (int unit = cluster_id; ok && unit < units; unit += n_clusters) {
         const int split = unit / tiles_mn;
         const int rem = unit - split * tiles_mn;
-        const int n_blk = p.n_fastest ? rem % p.n_tiles : rem / p.m_tiles;
-        const int m_blk = p.n_fastest ? rem / p.n_tiles : rem - n_blk * p.m_tiles;
+        int m_blk, n_blk;
+        unit_to_tile(p, rem, m_blk, n_blk);
         const int a_mn = p.a_mn0 + m_blk * PAIR_M + int(rank) * BLOCK_M;
         const int b_mn = p.b_mn0 + n_blk * BLOCK_N + int(rank) * HALF_N;
         if (!tile_selected(p, m_blk * PAIR_M, PAIR_M)) continue;
@@ -1055,7 +1086,8 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       for (int unit = cluster_id; ok && unit < units; unit += n_clusters) {
         if (p.run_mask != nullptr) {  // same tile selection as the producers and the epilogue warps
           const int rem = unit % tiles_mn;
-          const int m_sel = p.n_fastest ? rem / p.n_tiles : rem % p.m_tiles;
+          int m_sel, n_sel;
+          unit_to_tile(p, rem, m_sel, n_sel);
           if (!tile_selected(p, m_sel * PAIR_M, PAIR_M)) continue;
         }
         if (!mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
@@ -1109,8 +1141,8 @@ lce_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     for (int unit = cluster_id; unit < units; unit += n_clusters) {
       const int split = unit / tiles_mn;
       const int rem = unit - split * tiles_mn;
-      const int n_blk = p.n_fastest ? rem % p.n_tiles : rem / p.m_tiles;
-      const int m_blk = p.n_fastest ? rem / p.n_tiles : rem - n_blk * p.m_tiles;
+      int m_blk, n_blk;
+      unit_to_tile(p, rem, m_blk, n_blk);
       const int m_blk128 = m_blk * 2 + int(rank);  // this CTA's 128-row block
       if (!tile_selected(p, m_blk * PAIR_M, PAIR_M)) continue;
       if (!mbar_wait_warp(&sh->acc_full[acc], acc_phase, abort_flag)) {

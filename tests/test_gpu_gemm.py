@@ -22,7 +22,7 @@ def gemm_variant(request):
     SINGLE_CTA = 0
 
 
-def run(dtype, a_mn, b_mn, M, N, K, splits=1, seed=0):
+def run(dtype, a_mn, b_mn, M, N, K, splits=1, seed=0, raster_group=0, n_fastest=0):
     lib = _native.load()
     g = torch.Generator().manual_seed(seed)
     A = torch.randn(M, K, generator=g).to(dtype)
@@ -33,7 +33,7 @@ def run(dtype, a_mn, b_mn, M, N, K, splits=1, seed=0):
     out = torch.full((splits, M, N), float("nan"), dtype=torch.float32, device="cuda")
     status = torch.zeros(8, dtype=torch.int32, device="cuda")
     rc = lib.lce_debug_gemm(CODE[dtype], a_mn, b_mn, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
-                            out.data_ptr(), M, N, K, splits, SINGLE_CTA, status.data_ptr(),
+                            out.data_ptr(), M, N, K, splits, SINGLE_CTA, raster_group, n_fastest, status.data_ptr(),
                             torch.cuda.current_stream().cuda_stream)
     assert rc == 0, _native.status_string(rc)
     torch.cuda.synchronize()
@@ -62,13 +62,24 @@ def test_more_tiles_than_sms_and_long_k():
     #                                                                      (fp32 accumulation over K = 9600)
 
 
+@pytest.mark.parametrize("n_fastest", [0, 1])
+@pytest.mark.parametrize("group", [1, 2, 3, 5, 64])
+def test_banded_walk_over_the_tile_grid_visits_every_tile_once(group, n_fastest):
+    # 11 x 7 tiles of 128 x 256 (single CTA) or 5 x 7 of 256 x 256 (CTA pairs), two K splits; bands that do not
+    # divide the fast dimension and a band wider than the grid. The output starts as NaN: a tile that no unit
+    # visits fails the comparison, and so does one that holds another tile's product.
+    m_tiles = 11 if SINGLE_CTA else 10
+    assert run(torch.bfloat16, 0, 1, 128 * m_tiles, 256 * 7, 256, splits=2, raster_group=group,
+               n_fastest=n_fastest) < 1e-5
+
+
 def test_shape_errors_are_status_codes():
     lib = _native.load()
     t = torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda")
     o = torch.zeros(256, 256, dtype=torch.float32, device="cuda")
     s = torch.zeros(8, dtype=torch.int32, device="cuda")
     call = lambda m, n, k, sp=1: lib.lce_debug_gemm(1, 0, 0, t.data_ptr(), 256, t.data_ptr(), 256, o.data_ptr(), m, n,
-                                                    k, sp, SINGLE_CTA, s.data_ptr(), None)
+                                                    k, sp, SINGLE_CTA, 0, 0, s.data_ptr(), None)
     assert call(100, 256, 256) == -2
     assert call(128, 100, 256) == -2
     assert call(128, 256, 100) == -2
