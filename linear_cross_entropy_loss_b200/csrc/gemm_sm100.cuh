@@ -57,7 +57,7 @@ struct GemmShared {
 };
 
 // Output staging for TMA stores: each of the four epilogue warps owns two buffers of 32 rows x 128 bytes
-// (128-byte swizzle), filled from registers and drained by cp.async.bulk.tensor stores / reduce-adds.
+// (128-byte swizzle), filled from registers and drained by cp.async.bulk.tensor stores.
 constexpr int kStoreStageBytes = 32 * 128;
 constexpr int kStoreStagingBytes = 4 * 2 * kStoreStageBytes;  // 32 KiB per CTA
 
