@@ -300,9 +300,10 @@ int lce_profile_read(double* ms3, long long* launches3);
  * single_cta != 0: use the single-CTA kernel (128 x 256 tiles) even where the pass would use CTA pairs
  * (cta_group::2, 256 x 256 tiles; the pass falls back to the single-CTA kernel for an odd number of 128-row tiles).
  * raster_group, n_fastest: the order in which the persistent CTAs walk the tile grid. n_fastest != 0: along N first
- * (the dx contraction), else along M first (logits, dW). raster_group 0: as in the pass (no bands unless the
- * environment variable LCE_RASTER_GROUP asks for them), -1: no bands, -2: bands chosen from the shape, G > 0:
- * bands of G tiles. The result does not depend on either.
+ * (the dx contraction), else along M first (logits, dW). raster_group 0: as in the pass (bands of at most 4096
+ * rows when the fast dimension is longer, unless the environment variable LCE_RASTER_GROUP says otherwise),
+ * -1: no bands, -2: chosen from the shape whatever the environment says, G > 0: bands of G tiles. The result does
+ * not depend on either.
  * dev_status: int[8] device words, 8-byte aligned: [0] status (0 = ok); [2..3] int64 SM cycles and [4..5] int64
  * nanoseconds that CTA 0 spent in the kernel (their ratio is the SM clock the kernel ran at).
  * No counterpart in the reference. */

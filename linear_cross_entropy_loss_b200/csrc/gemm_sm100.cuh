@@ -72,8 +72,8 @@ struct GemmParams {
   int k_blocks;  // K-blocks (128 bytes of K each) per split
   int n_fastest; // 0: consecutive units walk M first (then N, then the K-split); 1: they walk N first
   int raster_group;  // kernels: 0 = walk the whole fast dimension, G > 0 = in bands of G tiles (unit_to_tile).
-                     // Given to launch_gemm: 0 = the process default (no bands unless LCE_RASTER_GROUP asks),
-                     // -1 = no bands, -2 = chosen from the shape, G > 0 = bands of G
+                     // Given to launch_gemm: 0 = the process default (chosen from the shape unless
+                     // LCE_RASTER_GROUP says otherwise), -1 = no bands, -2 = chosen from the shape, G > 0 = bands of G
   // element offsets added to the tensor-map coordinates
   int a_mn0, a_k0, b_mn0, b_k0;
 
@@ -694,8 +694,7 @@ __device__ __forceinline__ bool tile_selected(const GemmParams& p, int row0, int
 // whole fast dimension times a few slow tiles. With raster_group = G the fast dimension is cut into bands of G
 // tiles and each band is walked over the whole slow dimension before the next band starts: the units in flight
 // form a block of about G x (CTAs / G) tiles. When the fast dimension is long this block shares more operand rows
-// per byte fetched, and the band's operand (G tiles x K) can stay in L2 while the other operand streams past it,
-// instead of being fetched from DRAM again for every slow tile.
+// per byte fetched, and less of the band's operand (G tiles x K) is fetched from DRAM again for every slow tile.
 __device__ __forceinline__ void unit_to_tile(const GemmParams& p, int rem, int& m_blk, int& n_blk) {
   const int nf = p.n_fastest ? p.n_tiles : p.m_tiles;
   int f, s;

@@ -280,39 +280,35 @@ bool epilogue_tma_enabled() {
   return on;
 }
 
-// LCE_RASTER_GROUP (A/B measurements; read once per process): unset or "0" walks every tile grid without bands
-// (the default: bands measured 3-4 % slower on the shapes they apply to, see choose_raster_group), "auto" lets
-// choose_raster_group decide, a positive number forces bands of that many tiles.
+// LCE_RASTER_GROUP (A/B measurements; read once per process): unset or "auto" lets choose_raster_group decide,
+// "0" walks every tile grid without bands, a positive number forces bands of that many tiles.
 int raster_group_override() {
   static const int value = [] {
     const char* v = std::getenv("LCE_RASTER_GROUP");
-    if (v == nullptr || *v == 0) return -1;
-    if (std::strcmp(v, "auto") == 0) return 0;
+    if (v == nullptr || *v == 0 || std::strcmp(v, "auto") == 0) return -2;
     char* end = nullptr;
     const long g = std::strtol(v, &end, 10);
-    if (end == v || g <= 0 || g > (1 << 20)) return -1;
-    return (int)g;
+    if (end == v || g < 0 || g > (1 << 20)) return -2;
+    return g == 0 ? -1 : (int)g;
   }();
   return value;
 }
 
-// Bands for the walk over the tile grid (unit_to_tile); 0 = none. `fast_tiles` tiles of `fast_tile_rows` rows
-// lie along the dimension that consecutive units walk first, each reading k_blocks * 128 bytes per row, and
-// `in_flight` tiles are worked on at one time. Two reasons for bands: a block of in-flight tiles that is closer to
-// a square fetches fewer operand bytes per flop than a long thin one, and a band whose operand fits into L2
-// (32 MiB of the 126) is read from DRAM once per band instead of once per in-flight block. With the default
-// chunk of 4096 rows and hidden sizes up to 4096 no grid is long enough for either to matter and 0 comes back.
-// Measured on one B200, same call: N=131072 H=8192 V=262144 (bands of 8 in all three contractions) 940 TFLOP/s
-// with bands against 975 without; N=65536 H=4096 V=131072 (16 / 8 / 8) 1060 against 1094 -- L2 already keeps enough
-// of the long operand, so the walk without bands stays the default and this policy runs only when asked for.
-int choose_raster_group(int fast_tiles, long long fast_tile_rows, int k_blocks, int in_flight) {
-  const long long tile_bytes = fast_tile_rows * (long long)k_blocks * 128;
-  long long g = (32ll << 20) / (tile_bytes > 0 ? tile_bytes : 1);
-  int side = 1;
-  while ((side + 1) * (side + 1) <= in_flight) ++side;  // floor(sqrt(in_flight)): 8 for 74 clusters, 12 for 148 CTAs
-  if (g < side) g = side;
-  if (g >= fast_tiles) return 0;
-  const int bands = (int)((fast_tiles + g - 1) / g);
+// Bands for the walk over the tile grid (unit_to_tile); 0 = none. `fast_tiles` tiles of `fast_tile_rows` rows or
+// columns lie along the dimension that consecutive units walk first. A grid longer than 4096 rows (16 tiles of
+// the CTA-pair kernel) along that dimension is walked in equal bands of at most 4096 rows: the tiles in flight
+// then form the same 16 x 4.6 block as at the default chunk of 4096 rows, and less of the long operand is fetched
+// from DRAM again (forward at 8192 rows x 8192 hidden x 16384 columns, ncu: 2.5 GB read instead of 5.1 GB, of
+// 0.4 GB that exist). Measured on two B200s inside the power-capped step, TFLOP/s of the whole step without bands
+// / with bands of 8, 11, 16, 24 tiles (all three contractions have 32-tile grids in both shapes):
+//   N=131072 H=8192 V=262144 chunk 8192:  1054 / 1058, 1060, 1097, 1055    (bands of 4: 1022)
+//   N=65536  H=4096 V=131072 chunk 8192:  1211 / 1230, 1205, 1239, 1225
+// and the default shape (16-tile grids) with its forward cut into two bands of 8: 1236 against 1247. Why exactly
+// 16 wins is not understood (narrower bands fetch even fewer bytes); the rule keeps what was measured.
+int choose_raster_group(int fast_tiles, int fast_tile_rows) {
+  const int widest = 4096 / fast_tile_rows;  // 16 tiles of 256, 32 of 128
+  if (fast_tiles <= widest) return 0;
+  const int bands = (fast_tiles + widest - 1) / widest;
   return (fast_tiles + bands - 1) / bands;  // equal bands rather than a narrow last one
 }
 
@@ -376,14 +372,12 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
   const long long units = (long long)gp.splits * gp.n_tiles * gp.m_tiles;
   if (units <= 0 || units > (1ll << 30)) return LCE_ERR_TOO_LARGE;
   {
-    // 0: what LCE_RASTER_GROUP says (none unless set), -1: none, -2: from the shape, > 0: as given
+    // 0: what LCE_RASTER_GROUP says (from the shape unless set), -1: none, -2: from the shape, > 0: as given
     int want = gp.raster_group;
-    if (want == 0) want = raster_group_override() == 0 ? -2 : raster_group_override();
-    if (want == -2) {
-      const int in_flight = pair ? sms / 2 : sms;
-      want = gp.n_fastest ? choose_raster_group(gp.n_tiles, BLOCK_N, gp.k_blocks, in_flight)
-                          : choose_raster_group(gp.m_tiles, pair ? 2 * BLOCK_M : BLOCK_M, gp.k_blocks, in_flight);
-    }
+    if (want == 0) want = raster_group_override();
+    if (want == -2)
+      want = gp.n_fastest ? choose_raster_group(gp.n_tiles, BLOCK_N)
+                          : choose_raster_group(gp.m_tiles, pair ? 2 * BLOCK_M : BLOCK_M);
     gp.raster_group = want > 0 ? want : 0;
   }
   if (pair) {

@@ -56,6 +56,9 @@ CONFIGS = {
     # then runs once writing and once accumulating)
     "profile_small_fp16": Config("profile_small_fp16", 4096, 2048, 32768, torch.float16, 4096, seed=6),
     "profile_small_2chunks_bf16": Config("profile_small_2chunks_bf16", 8192, 2048, 32768, torch.bfloat16, 4096, seed=6),
+    # long tile grids for profiler captures (32 row tiles per chunk, an x chunk of 128 MiB that cannot stay in L2
+    # beside the streamed weight): the shape class of the large-hidden configurations at a vocabulary of 16384
+    "profile_wide_bf16": Config("profile_wide_bf16", 8192, 8192, 16384, torch.bfloat16, 8192, seed=6),
     # the headline metric's point: default shape in bf16, options off
     "headline_bf16": Config("headline_bf16", 16384, 2048, 131072, torch.bfloat16, 4096, seed=1),
 }
