@@ -241,6 +241,11 @@ class ShardSpec:
 # of one sub-chunk runs on a second stream underneath the tensor-core kernels of the other.
 SUBCHUNKS = 2
 MIN_SPLIT_ELEMS = 1 << 25  # slab elements of a chunk from which halving pays (equal on all ranks of a sharded run)
+# Rows a half must keep. Measured inside the power-capped step (fp16, per-tile slabs, same call): chunks of 8192
+# rows as two halves 193.4 ms per step against 196.0 whole (N=65536, H=4096, V=131072), but chunks of 4096 rows as two
+# halves 24.5-24.8 ms against 24.0-24.6 whole at the default shape (23.5 / 23.1 on another GPU): a half of 2048 rows
+# streams the weight a second time for too little work to hide.
+MIN_HALF_ROWS = 4096
 _side_streams: dict = {}
 
 
@@ -255,7 +260,7 @@ def _split_rows(row0: int, rows: int, split: bool):
     """Sub-chunks of a chunk: halves when each half keeps the 256-row granularity of the CTA-pair kernels.
     Only the per-tile slab mode has a slab-wide transform worth hiding; the default mode of bf16 / fp32 runs a
     chunk as one piece."""
-    if split and SUBCHUNKS == 2 and rows >= 1024 and rows % 512 == 0:
+    if split and SUBCHUNKS == 2 and rows >= 2 * MIN_HALF_ROWS and rows % 512 == 0:
         return [(row0, rows // 2), (row0 + rows // 2, rows // 2)]
     return [(row0, rows)]
 

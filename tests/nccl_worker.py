@@ -23,6 +23,7 @@ def main():
     dist.init_process_group("nccl")
     from linear_cross_entropy_loss_b200 import ops
     ops.MIN_SPLIT_ELEMS = 0  # the fp16 case below must exercise half chunks on two streams at this small size
+    ops.MIN_HALF_ROWS = 512
     N, H, V = 1024, 512, 8192
     vl = V // world
     ok = True

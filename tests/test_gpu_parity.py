@@ -394,13 +394,14 @@ def test_randomised_shapes_options_and_modes(seed, monkeypatch):
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_half_chunks_on_two_streams_at_a_small_size(monkeypatch, dtype):
     """Per-tile slabs run a chunk as two halves, the slab pass of one half on a second stream under the contractions of
-    the other. The library only does that from 2^25 slab elements per chunk on; here the threshold is lifted so that
+    the other. The library only does that from 2^25 slab elements and 8192 rows per chunk on; here both limits are lifted so that
     the two-stream path is checked against the oracle at a size the oracle can do, and against the one-stream pass."""
     from linear_cross_entropy_loss_b200 import ops
     monkeypatch.setenv("LCE_SLAB_MODE", "tile")
     x, y, W = random_problem(2048, 256, 4096, dtype, seed=31)
     whole = run_gpu(x, y, W, -1, 1e-4, 0.5, 1024, True)
     monkeypatch.setattr(ops, "MIN_SPLIT_ELEMS", 0)
+    monkeypatch.setattr(ops, "MIN_HALF_ROWS", 512)
     check_against_oracle(x, y, W, dtype, ignore=-1, zreg=1e-4, scale=0.5, chunk=1024)
     halves = run_gpu(x, y, W, -1, 1e-4, 0.5, 1024, True)
     assert abs(halves[0][0] - whole[0][0]) <= 1e-6 * abs(whole[0][0])

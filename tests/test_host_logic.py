@@ -294,6 +294,7 @@ def test_collective_sequence_of_a_sharded_pass_does_not_depend_on_the_slab_mode(
     x, y, W = make(N=2048, H=256, V=512)
     x, W = x.to(dtype), W.to(dtype)
     monkeypatch.setattr(ops, "MIN_SPLIT_ELEMS", 0)  # halve chunks even at this toy size
+    monkeypatch.setattr(ops, "MIN_HALF_ROWS", 512)
 
     def sequence(mode):
         monkeypatch.setattr(ops.slab_mode_policy, "choose",
