@@ -241,10 +241,10 @@ class ShardSpec:
 # of one sub-chunk runs on a second stream underneath the tensor-core kernels of the other.
 SUBCHUNKS = 2
 MIN_SPLIT_ELEMS = 1 << 25  # slab elements of a chunk from which halving pays (equal on all ranks of a sharded run)
-# Rows a half must keep. Measured inside the power-capped step (fp16, per-tile slabs, same call): chunks of 8192
-# rows as two halves 193.4 ms per step against 196.0 whole (N=65536, H=4096, V=131072), but chunks of 4096 rows as two
-# halves 24.5-24.8 ms against 24.0-24.6 whole at the default shape (23.5 / 23.1 on another GPU): a half of 2048 rows
-# streams the weight a second time for too little work to hide.
+# Rows a half must keep. Measured inside the power-capped step (fp16, per-tile slabs, A/B inside one call): chunks
+# of 8192 rows as two halves 193.4 ms per step against 196.0 whole (N=65536, H=4096, V=131072); chunks of 4096 rows
+# as two halves between 2 % slower and 1 % faster than whole over four calls at the default shape (a half of 2048
+# rows streams the weight a second time), with 56 instead of 32 launches per step and no single-call pass.
 MIN_HALF_ROWS = 4096
 _side_streams: dict = {}
 
