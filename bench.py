@@ -345,7 +345,8 @@ def config_dict(cfg, n_gpus, args):
         "dx_exchange": ("none" if n_gpus == 1 else
                         "peer stores fused into the dx contraction" if os.environ.get("LCE_PEER_DX") == "1"
                         else "NCCL all-reduce per chunk, in stream order" if os.environ.get("LCE_DX_REDUCE") == "chunk"
-                        else "one NCCL all-reduce of dx per pass"),
+                        else "one NCCL all-reduce of dx per pass"
+                        + (" (fp32 partial sums for fp16 inputs)" if str(cfg.dtype) == "torch.float16" else "")),
         "row_partials_exchange": ("none" if n_gpus == 1 else
                                   "NCCL all-gather per chunk" if (os.environ.get("LCE_PEER_PARTS", "0") != "1"
                                                                   or os.environ.get("LCE_PEER_DX") == "1")

@@ -419,8 +419,6 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     row_parts = torch.empty(ROW_PARTS * N_group, dtype=torch.float32, device=dev)
     out5 = torch.empty(5, dtype=torch.float32, device=dev)
     dx = dW = dW_res = None
-    if want_dx:
-        dx = torch.empty((N, H), dtype=x.dtype, device=dev)
     if want_dW:
         dW = _aligned_rows_like((H, V), At.dtype, dev)
         if n_chunks > 1 and At.dtype != torch.float32:
@@ -443,6 +441,14 @@ def run_pass(x, y, At, ignore_index, z_regularization, logit_scale, N_chunk_size
     if shard is not None and want_dx and shard.peer_exchange is not None and parts is None:
         peer = shard.peer_exchange(prob, x.dtype)
     dx_once = shard is not None and shard.reduce_dx_once and peer is None
+    if want_dx:
+        # fp16 partial sums that an all-reduce adds up travel as fp32: with dx around 1e-6 (1 / n_valid) every rank's
+        # partial would otherwise be rounded to fp16's absolute spacing of 6e-8 before the sum (measured on 2 GPUs at
+        # the default shape: cosine to the float64 dx 0.99986, against 0.99991 for the one rounding an fp16 result
+        # needs anyway). The caller's backward converts while it applies grad_output (_scaled_grads). bf16 has the
+        # exponent range of fp32 and the peer exchange sums in fp32 itself, so both keep the input type.
+        wide = shard is not None and peer is None and x.dtype == torch.float16
+        dx = torch.empty((N, H), dtype=torch.float32 if wide else x.dtype, device=dev)
 
     peer_done = []
     xstream = None
@@ -588,8 +594,14 @@ def _scaled_grads(ctx, grad_output):
     dev = dx.device if dx is not None else dW.device
     factor = grad_output.detach().reshape(1).to(device=dev, dtype=torch.float32).contiguous()
     if dx is not None:
-        backend.grad_scale_cast(dx, dx, factor)
-        dx = dx.view(ctx.lce_x_shape)
+        dx_dtype = getattr(ctx, "lce_x_dtype", dx.dtype)
+        if dx.dtype != dx_dtype:  # fp32 sums of a sharded fp16 pass (run_pass): scale and convert in one kernel
+            narrow = _aligned_rows_like(tuple(dx.shape), dx_dtype, dev)
+            backend.grad_scale_cast(dx, narrow, factor)
+            dx = narrow
+        else:
+            backend.grad_scale_cast(dx, dx, factor)
+        dx = dx.reshape(ctx.lce_x_shape)
     if dW is not None:
         backend.grad_scale_cast(dW, dW, factor)
     return dx, dW
@@ -612,6 +624,7 @@ class LinearXentImplementation(torch.autograd.Function):
                                            monitoring, want)
             ctx.lce_grads = (dx, dA) if any(want) else None
             ctx.lce_x_shape = x_in.shape
+            ctx.lce_x_dtype = x.dtype
             loss, z_value, logit_max, logit_ent, logit_norm = out5.unbind(0)
             ctx.mark_non_differentiable(z_value, logit_max, logit_ent, logit_norm)
             return loss, z_value, logit_max, logit_ent, logit_norm

@@ -223,6 +223,7 @@ class VocabShardedLinearXent(torch.autograd.Function):
                 coll.wait_all()
             ctx.lce_grads = (dx, dA) if any(want) else None
             ctx.lce_x_shape = x_in.shape
+            ctx.lce_x_dtype = x.dtype
             loss, z_value, logit_max, logit_ent, logit_norm = out5.unbind(0)
             ctx.mark_non_differentiable(z_value, logit_max, logit_ent, logit_norm)
             return loss, z_value, logit_max, logit_ent, logit_norm

@@ -394,3 +394,26 @@ def test_export_names_of_the_reference_package():
 
     for name in ["fwd_configs", "bwd_configs", "LinearCrossEntropyLoss", "linear_cross_entropy"]:
         assert hasattr(pkg, name)
+
+
+def test_sharded_fp16_pass_sums_dx_in_fp32_and_hands_back_fp16(fake):
+    """Every rank's dx of a sharded pass is a partial sum that an all-reduce adds up. For fp16 these travel as fp32
+    (values around 1 / n_valid sit in fp16's subnormal range, and one rounding per rank would add up); backward
+    converts while it applies grad_output. bf16 keeps its type."""
+    from types import SimpleNamespace
+
+    for dtype, carried in ((torch.float16, torch.float32), (torch.bfloat16, torch.bfloat16)):
+        x, y, W = make(N=512, H=256, V=512, dtype=dtype)
+        reduced = []
+        shard = ops.ShardSpec(rank=0, world=1, vocab_offset=0, gather_row_parts=lambda t: t,
+                              reduce_dx=lambda rows: reduced.append((rows.dtype, tuple(rows.shape))), reduce_dx_once=True)
+        out5, dx, dW, _ = ops.run_pass(x, y, W, -1, 0.0, 1.0, 256, False, True, shard=shard)
+        assert dx.dtype == carried and reduced == [(carried, (512, 256))]
+        assert dW.dtype == dtype
+        ctx = SimpleNamespace(lce_grads=(dx.clone(), None), lce_x_shape=(2, 256, 256), lce_x_dtype=dtype)
+        gx, gW = ops._scaled_grads(ctx, torch.tensor(2.0))
+        assert gW is None and gx.dtype == dtype and gx.shape == (2, 256, 256)
+        assert torch.allclose(gx.double().reshape(512, 256), 2.0 * dx.double(), rtol=1e-2, atol=1e-7)
+    # without sharding nothing changes: fp16 in, fp16 out of run_pass
+    x, y, W = make(N=512, H=256, V=512, dtype=torch.float16)
+    assert ops.run_pass(x, y, W, -1, 0.0, 1.0, 256, False, True)[1].dtype == torch.float16
